@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SMOL_LM_ABI_VERSION 2
+#define SMOL_LM_ABI_VERSION 3
 
 enum { SMOL_LM_BF16 = 0, SMOL_LM_F32 = 1 };
 /* token mixers */
@@ -32,7 +32,9 @@ enum {
     SMOL_LM_MIX_GENERAL_DELTA = 1,     /* generalized delta rule, state [dim, dim] per head */
     SMOL_LM_MIX_LATENT_ATTENTION = 2,  /* attention through a cached latent: queries and keys/values are low-rank, part of each
                                           head's query/key is rotated by position, one gate per head */
-    SMOL_LM_MIX_GATED_LINEAR = 3       /* linear attention with a decay per key channel, state [dim, vdim] per head */
+    SMOL_LM_MIX_GATED_LINEAR = 3,      /* linear attention with a decay per key channel, state [dim, vdim] per head */
+    SMOL_LM_MIX_STATE_SPACE = 4        /* state-space recurrence with one decay per head and step: a short causal convolution in
+                                          front, state [n_state, vdim] per head plus the convolution's last inputs in the slot */
 };
 /* feed-forward kinds */
 enum {
@@ -42,7 +44,13 @@ enum {
     SMOL_LM_MLP_EXPERTS = 3            /* routed mixture of gated experts, some router outputs standing for the input itself */
 };
 /* activations of the gated feed-forwards */
-enum { SMOL_LM_ACT_GELU_TANH = 0, SMOL_LM_ACT_SILU = 1 };
+enum {
+    SMOL_LM_ACT_GELU_TANH = 0,
+    SMOL_LM_ACT_SILU = 1,
+    SMOL_LM_ACT_CLAMPED = 2            /* g = min(gate, limit), u = clamp(up, -limit, limit): g * sigmoid(act_alpha * g) * (u + 1) */
+};
+/* how a router turns its logits into scores */
+enum { SMOL_LM_ROUTE_SOFTMAX = 0, SMOL_LM_ROUTE_SIGMOID = 1 };
 /* how a layer wraps its sublayers */
 enum {
     SMOL_LM_BLOCK_SANDWICH = 0,        /* x += ls * norm_b(sublayer(norm_a(x))): norms with one-plus weight vectors, layer scales */
@@ -98,6 +106,35 @@ typedef struct SmolLmLayer {
     const float* w_router;    /* routed: [n_experts + n_identity][width] fp32 */
     const float* route_bias;  /* routed: added to the scores for the choice only [n_experts + n_identity] */
     const float* depth_mix;   /* post-norm block: weights of the embedding output and of every layer result so far [run + 2] */
+    /* --- options of the softmax attention (SMOL_LM_MIX_SINK_ATTENTION) --- */
+    int32_t window;           /* a query at position i sees the keys 0 <= i - j < window (0: every earlier key) */
+    int32_t norm_whole;       /* 1: q_norm [heads * dim] and k_norm [kv_heads * dim] act over the whole projection (one root
+                                 mean square for all heads) instead of per head */
+    int32_t no_gate;          /* 1: the input projection holds no gate rows and the result is not gated */
+    float softcap;            /* score <- softcap * tanh(score / softcap) after the scale (0: none) */
+    const float* dist_slope;  /* linear distance penalty slope * (i - j) taken off the score, [heads] (NULL: none) */
+    /* --- every mixer --- */
+    const float* in_bias;     /* bias of the fused input projection [rows of w_in] (NULL: none) */
+    const float* out_bias;    /* added to the output projection's result [width] (NULL: none) */
+    float mix_scale;          /* multiplies the mixer's result before the output projection (0 reads as 1) */
+    /* A second mixer that runs beside this one on the same input (HOST pointer, copied by create; NULL: none).  Only its
+     * mixer fields are read.  w_in then holds the rows of this mixer followed by the side mixer's, in_bias likewise, and
+     * w_out is [width, this mixer's columns + the side mixer's columns]: the two results, each times its mix_scale, are
+     * summed by the one output projection.  Softmax attention and the state-space recurrence can be paired. */
+    const struct SmolLmLayer* side;
+    /* --- state-space recurrence: w_in rows are gate z [heads*vdim] | x [heads*vdim] | B [bc_groups*n_state] | C [likewise] | dt [heads];
+     *     x, B and C pass a causal convolution per channel and silu; dt = softplus(dt + dt_bias); per head (sharing B and C
+     *     with the heads of its group)  S <- exp(-exp(a_log) dt) S + dt B x^T,  y = S^T C + skip * x;  then y * silu(z), an RMS
+     *     division in norm_parts equal parts of the heads*vdim channels, times out_norm [heads*vdim] --- */
+    int32_t n_state, bc_groups, conv_taps, norm_parts;
+    const float* conv_w;      /* [heads*vdim + 2*bc_groups*n_state][conv_taps], the last tap multiplies the current token */
+    const float* conv_b;      /* [heads*vdim + 2*bc_groups*n_state] */
+    const float *dt_bias, *a_log, *skip;   /* [heads] each */
+    /* --- feed-forward options --- */
+    float act_limit, act_alpha;   /* SMOL_LM_ACT_CLAMPED */
+    int32_t router_score;     /* SMOL_LM_ROUTE_* (route_bias may be NULL) */
+    int32_t router_plain;     /* 1: a chosen output's weight is its score itself, not the score over the chosen scores' sum */
+    int32_t route_input;      /* 1: the weight multiplies the expert's input rather than its output */
 } SmolLmLayer;
 
 typedef struct SmolLmConfig {
@@ -115,6 +152,7 @@ typedef struct SmolLmConfig {
     int32_t block;            /* SMOL_LM_BLOCK_* */
     float residual_alpha;     /* post-norm block: multiplies the stream before the sublayer's output is added */
     float logit_scale;        /* multiplies the logits */
+    int32_t norm_plain;       /* sandwich block: 1 = the norms' weight vectors are used as they are, 0 = one is added to them */
 } SmolLmConfig;
 
 typedef struct SmolLmGlobals {
@@ -152,7 +190,7 @@ int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers, const int
 void smol_lm_destroy(SmolLm* m);
 
 size_t smol_lm_page_bytes(const SmolLm* m);       /* one page: page_size positions of every attention run's keys and values (or latents) */
-size_t smol_lm_slot_bytes(const SmolLm* m);       /* one slot: the fp32 matrix states of every recurrent run */
+size_t smol_lm_slot_bytes(const SmolLm* m);       /* one slot: the fp32 matrix states (and convolution inputs) of every recurrent run */
 size_t smol_lm_workspace_bytes(const SmolLm* m);
 
 int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace, size_t workspace_bytes, void* d_pages, int32_t n_pages,

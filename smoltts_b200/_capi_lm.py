@@ -11,26 +11,37 @@ import os
 from . import build as _build
 from ._errors import SMOL_OK, SmolError
 
-SMOL_LM_ABI_VERSION = 2
+SMOL_LM_ABI_VERSION = 3
 SMOL_LM_BF16, SMOL_LM_F32 = 0, 1
 
 
 class SmolLmLayer(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "rank", "mlp", "ff")] + [
-        (n, C.c_float) for n in ("score_scale", "decay_coef", "unit_eps")] + [
-        (n, C.c_void_p) for n in ("w_in", "w_out", "w_up", "w_down", "norm1", "norm1b", "norm2", "norm2b", "ls1", "ls2",
-                                  "q_norm", "k_norm", "dist_r1", "dist_r2", "sink", "rate_bias", "decay_w2", "decay_bias",
-                                  "out_norm", "act")] + [
-        (n, C.c_int32) for n in ("rot_dim", "rot_dims", "q_rank", "kv_rank", "mlp_act", "n_experts", "n_identity", "top_k", "n_groups", "keep_groups")] + [
-        (n, C.c_float) for n in ("rot_base", "decay_tau", "router_scale")] + [
-        (n, C.c_void_p) for n in ("w_q_up", "w_k_up_t", "w_v_up", "q_lat_norm", "kv_lat_norm", "w_experts_in", "w_experts_out", "w_router",
-                                  "route_bias", "depth_mix")]
+    pass
+
+
+# `side` points to another SmolLmLayer (host memory), so the fields are set after the class exists
+SmolLmLayer._fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "rank", "mlp", "ff")] + [
+    (n, C.c_float) for n in ("score_scale", "decay_coef", "unit_eps")] + [
+    (n, C.c_void_p) for n in ("w_in", "w_out", "w_up", "w_down", "norm1", "norm1b", "norm2", "norm2b", "ls1", "ls2",
+                              "q_norm", "k_norm", "dist_r1", "dist_r2", "sink", "rate_bias", "decay_w2", "decay_bias",
+                              "out_norm", "act")] + [
+    (n, C.c_int32) for n in ("rot_dim", "rot_dims", "q_rank", "kv_rank", "mlp_act", "n_experts", "n_identity", "top_k", "n_groups", "keep_groups")] + [
+    (n, C.c_float) for n in ("rot_base", "decay_tau", "router_scale")] + [
+    (n, C.c_void_p) for n in ("w_q_up", "w_k_up_t", "w_v_up", "q_lat_norm", "kv_lat_norm", "w_experts_in", "w_experts_out", "w_router",
+                              "route_bias", "depth_mix")] + [
+    (n, C.c_int32) for n in ("window", "norm_whole", "no_gate")] + [("softcap", C.c_float)] + [
+    (n, C.c_void_p) for n in ("dist_slope", "in_bias", "out_bias")] + [("mix_scale", C.c_float), ("side", C.POINTER(SmolLmLayer))] + [
+    (n, C.c_int32) for n in ("n_state", "bc_groups", "conv_taps", "norm_parts")] + [
+    (n, C.c_void_p) for n in ("conv_w", "conv_b", "dt_bias", "a_log", "skip")] + [
+    (n, C.c_float) for n in ("act_limit", "act_alpha")] + [
+    (n, C.c_int32) for n in ("router_score", "router_plain", "route_input")]
 
 
 class SmolLmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("dtype", "vocab", "width", "n_layers", "n_runs", "page_size", "max_step_tokens",
                                          "max_step_seqs", "max_want", "max_context", "use_graph")] + [
-        ("embed_scale", C.c_float), ("norm_eps", C.c_float), ("block", C.c_int32), ("residual_alpha", C.c_float), ("logit_scale", C.c_float)]
+        ("embed_scale", C.c_float), ("norm_eps", C.c_float), ("block", C.c_int32), ("residual_alpha", C.c_float), ("logit_scale", C.c_float),
+        ("norm_plain", C.c_int32)]
 
 
 class SmolLmGlobals(C.Structure):

@@ -56,10 +56,11 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Embedding: x[t] = embed[token[t]] * scale, then the first layer's norm (one-plus weight) -> hn.
+// Embedding: x[t] = embed[token[t]] * scale, then the first layer's norm -> hn.  The norms of the sandwich block multiply
+// by woff + w: woff = 1 for one-plus weight vectors, 0 for plain ones.
 template <class T>
 __global__ void embed_norm_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ embed, float scale, int D, int vocab,
-                                  const float* __restrict__ wn, float eps, float* __restrict__ x, T* __restrict__ hn) {
+                                  const float* __restrict__ wn, float eps, float* __restrict__ x, T* __restrict__ hn, const float woff) {
     __shared__ float red[33];
     const int t = blockIdx.x;
     int tok = tokens[t];
@@ -73,13 +74,13 @@ __global__ void embed_norm_kernel(const int32_t* __restrict__ tokens, const T* _
     }
     ss = block_sum(ss, red);
     const float r = 1.0f / sqrtf(ss / (float)D + eps);
-    for (int c = threadIdx.x; c < D; c += blockDim.x) hn[(size_t)t * D + c] = from_f<T>(x[(size_t)t * D + c] * r * (1.0f + wn[c]));
+    for (int c = threadIdx.x; c < D; c += blockDim.x) hn[(size_t)t * D + c] = from_f<T>(x[(size_t)t * D + c] * r * (woff + wn[c]));
 }
 
-// RMS norm of selected rows (one-plus weight) -> T.  rows == nullptr: row r of the output is row r of the input.
+// RMS norm of selected rows -> T.  rows == nullptr: row r of the output is row r of the input.
 template <class T>
 __global__ void norm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ w, float eps,
-                                 int D, T* __restrict__ out) {
+                                 int D, T* __restrict__ out, const float woff) {
     __shared__ float red[33];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
@@ -87,17 +88,19 @@ __global__ void norm_rows_kernel(const float* __restrict__ x, const int32_t* __r
     for (int c = threadIdx.x; c < D; c += blockDim.x) ss += xr[c] * xr[c];
     ss = block_sum(ss, red);
     const float s = 1.0f / sqrtf(ss / (float)D + eps);
-    for (int c = threadIdx.x; c < D; c += blockDim.x) out[(size_t)r * D + c] = from_f<T>(xr[c] * s * (1.0f + w[c]));
+    for (int c = threadIdx.x; c < D; c += blockDim.x) out[(size_t)r * D + c] = from_f<T>(xr[c] * s * (woff + w[c]));
 }
 
 // End of a sublayer fused with the start of the next one:
-//   x <- x + ls * (y / rms(y) * (1 + wb));   hn <- x / rms(x) * (1 + wn)     (wn == nullptr: no next norm)
-// One block per row; the new row is kept in shared memory between the two passes.
+//   x <- x + ls * (y / rms(y) * (woff + wb));   hn <- x / rms(x) * (woff + wn)     (wn == nullptr: no next norm)
+// yb != nullptr: a bias [D] joins y first (the output projection's).  One block per row; the new row is kept in shared
+// memory between the two passes.
 constexpr int kRowRegs = 8;   // add_norm keeps a row in registers when it has at most 8 elements per thread
 
 template <class T>
 __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
-                                const float* __restrict__ ls, const float* __restrict__ wn, float eps, int D, T* __restrict__ hn) {
+                                const float* __restrict__ ls, const float* __restrict__ wn, float eps, int D, T* __restrict__ hn,
+                                const float woff, const float* __restrict__ yb) {
     extern __shared__ float row[];
     __shared__ float red[33];
     const size_t o = (size_t)blockIdx.x * D;
@@ -109,7 +112,7 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
         for (int i = 0; i < kRowRegs; ++i) {
             const int c = threadIdx.x + i * blockDim.x;
             const bool in = c < D;
-            yv[i] = in ? y[o + c] : 0.0f;
+            yv[i] = in ? y[o + c] + (yb ? yb[c] : 0.0f) : 0.0f;
             xv[i] = in ? x[o + c] : 0.0f;
             lv[i] = in ? ls[c] : 0.0f;
             bv[i] = in ? wb[c] : 0.0f;
@@ -122,7 +125,7 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
 #pragma unroll
         for (int i = 0; i < kRowRegs; ++i) {
             const int c = threadIdx.x + i * blockDim.x;
-            const float v = xv[i] + lv[i] * (yv[i] * r * (1.0f + bv[i]));
+            const float v = xv[i] + lv[i] * (yv[i] * r * (woff + bv[i]));
             xv[i] = v;
             if (c < D) {
                 x[o + c] = v;
@@ -135,17 +138,17 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
 #pragma unroll
         for (int i = 0; i < kRowRegs; ++i) {
             const int c = threadIdx.x + i * blockDim.x;
-            if (c < D) hn[o + c] = from_f<T>(xv[i] * r2 * (1.0f + nv[i]));
+            if (c < D) hn[o + c] = from_f<T>(xv[i] * r2 * (woff + nv[i]));
         }
         return;
     }
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) { const float v = y[o + c]; ss += v * v; }
+    for (int c = threadIdx.x; c < D; c += blockDim.x) { const float v = y[o + c] + (yb ? yb[c] : 0.0f); ss += v * v; }
     ss = block_sum(ss, red);
     const float r = 1.0f / sqrtf(ss / (float)D + eps);
     float s2 = 0.0f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        const float v = x[o + c] + ls[c] * (y[o + c] * r * (1.0f + wb[c]));
+        const float v = x[o + c] + ls[c] * ((y[o + c] + (yb ? yb[c] : 0.0f)) * r * (woff + wb[c]));
         x[o + c] = v;
         row[c] = v;
         s2 += v * v;
@@ -153,7 +156,7 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
     if (!wn) return;
     s2 = block_sum(s2, red);
     const float r2 = 1.0f / sqrtf(s2 / (float)D + eps);
-    for (int c = threadIdx.x; c < D; c += blockDim.x) hn[o + c] = from_f<T>(row[c] * r2 * (1.0f + wn[c]));
+    for (int c = threadIdx.x; c < D; c += blockDim.x) hn[o + c] = from_f<T>(row[c] * r2 * (woff + wn[c]));
 }
 
 // Three sums over the block at once; every thread gets the results.  `red` holds 3 x 33 floats.
@@ -568,7 +571,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 // row (a latent that serves as both).  Optional per head: a distance penalty r1 ln(1 + r2 (i - j)) taken off the score
 // (r1 == nullptr: none) and a key-less sink logit in the softmax denominator (sink == nullptr: none).  The output is
 // multiplied by sigmoid(proj[t][gate_off + h * gate_ld + c * gate_step]): a gate per channel or (gate_step 0) per head.
-// Sink attention's proj row layout: q [H*d] | k [G*d] | v [G*dv] | gate [H*dv].
+// Sink attention's proj row layout: q [H*d] | k [G*d] | v [G*dv] | gate [H*dv] (no gate rows with has_gate == 0).
+// Further options, each off at its zero value: `bias` added to the projection's rows as they are read; `window` > 0 limits
+// a query at position i to the keys 0 <= i - j < window; `softcap` > 0 bends the scaled score to softcap * tanh(score /
+// softcap) before the penalties; `slope` takes slope_h * (i - j) off.  The result is multiplied by out_scale and written
+// with the row stride out_ld (two mixers side by side share one buffer).
 struct AttnArgs {
     const float* proj;
     int n_in;
@@ -586,7 +593,26 @@ struct AttnArgs {
     const int32_t* seq_start;
     int split_len, n_splits, short_rows;   // few-token path: key range per block, ranges per row, rows = sequences x kShortSeq
     float* part;                           // [short_rows][H][n_splits][dv + 2]: running maximum, denominator, unnormalised output
+    const float *bias, *slope;
+    int window, has_gate, out_ld;
+    float softcap, out_scale;
 };
+
+// first key a query at `pos` sees
+__device__ __forceinline__ int attn_first_key(const AttnArgs& A, int pos) { return A.window > 0 ? max(0, pos - A.window + 1) : 0; }
+
+// what follows the dot product: scale, soft cap, distance penalties.  FAST: hardware exponential / logarithm (bf16 engine).
+template <bool FAST>
+__device__ __forceinline__ float attn_score(const AttnArgs& A, float dot, int dist, float r1, float r2, float slope) {
+    float s = dot * A.scale;
+    if (A.softcap > 0.0f) {
+        const float z = s / A.softcap;
+        s = A.softcap * (FAST ? 1.0f - 2.0f / (__expf(2.0f * z) + 1.0f) : tanhf(z));
+    }
+    if (A.r1) s -= r1 * (FAST ? __logf(1.0f + r2 * (float)dist) : log1pf(r2 * (float)dist));
+    if (A.slope) s -= slope * (float)dist;
+    return s;
+}
 
 // One warp per (token, slot): slots 0..H-1 norm a query head into qbuf, H..H+G-1 norm a key head into the pool,
 // H+G..H+2G-1 copy a value head into the pool.
@@ -600,11 +626,12 @@ __global__ void attn_prep_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __re
     const float* row = A.proj + (size_t)t * A.n_in;
     if (s < A.H) {
         const float* q = row + s * A.d;
+        const float* qb = A.bias ? A.bias + s * A.d : nullptr;
         float ss = 0.0f;
-        for (int c = lane; c < A.d; c += 32) ss += q[c] * q[c];
+        for (int c = lane; c < A.d; c += 32) { const float v = q[c] + (qb ? qb[c] : 0.0f); ss += v * v; }
         ss = warp_sum(ss);
         const float r = 1.0f / sqrtf(ss / (float)A.d + A.eps);
-        for (int c = lane; c < A.d; c += 32) qbuf[((size_t)t * A.H + s) * A.d + c] = from_f<T>(q[c] * r * A.q_norm[c]);
+        for (int c = lane; c < A.d; c += 32) qbuf[((size_t)t * A.H + s) * A.d + c] = from_f<T>((q[c] + (qb ? qb[c] : 0.0f)) * r * A.q_norm[c]);
         return;
     }
     const int pos = A.tok_pos[t];
@@ -618,17 +645,58 @@ __global__ void attn_prep_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __re
     if (s < A.H + A.G) {
         const int gk = s - A.H;
         const float* k = row + A.H * A.d + gk * A.d;
+        const float* kb = A.bias ? A.bias + A.H * A.d + gk * A.d : nullptr;
         float ss = 0.0f;
-        for (int c = lane; c < A.d; c += 32) ss += k[c] * k[c];
+        for (int c = lane; c < A.d; c += 32) { const float v = k[c] + (kb ? kb[c] : 0.0f); ss += v * v; }
         ss = warp_sum(ss);
         const float r = 1.0f / sqrtf(ss / (float)A.d + A.eps);
         T* dst = base + A.k_off + ((size_t)gk * A.page_size + in_pg) * A.d;
-        for (int c = lane; c < A.d; c += 32) dst[c] = from_f<T>(k[c] * r * A.k_norm[c]);
+        for (int c = lane; c < A.d; c += 32) dst[c] = from_f<T>((k[c] + (kb ? kb[c] : 0.0f)) * r * A.k_norm[c]);
     } else {
         const int gv = s - A.H - A.G;
         const float* v = row + (A.H + A.G) * A.d + gv * A.dv;
+        const float* vb = A.bias ? A.bias + (A.H + A.G) * A.d + gv * A.dv : nullptr;
         T* dst = base + A.v_off + ((size_t)gv * A.page_size + in_pg) * A.dv;
-        for (int c = lane; c < A.dv; c += 32) dst[c] = from_f<T>(v[c]);
+        for (int c = lane; c < A.dv; c += 32) dst[c] = from_f<T>(v[c] + (vb ? vb[c] : 0.0f));
+    }
+}
+
+// The same preparation with query and key norms over the WHOLE projection: one root mean square for all query heads of a
+// token (weights q_norm [H*d]) and one for all key heads (k_norm [G*d]).  One block per token.
+template <class T>
+__global__ void attn_prep_whole_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __restrict__ pool) {
+    __shared__ float red[2][33];
+    const int t = blockIdx.x, nq = A.H * A.d, nk = A.G * A.d, nv = A.G * A.dv;
+    const float* row = A.proj + (size_t)t * A.n_in;
+    const int pos = A.tok_pos[t];
+    const int pg = pos / A.page_size, in_pg = pos % A.page_size;
+    const int page = pg < A.max_pages ? A.block_table[(size_t)A.tok_seq[t] * A.max_pages + pg] : -1;
+    auto at = [&](int c) { return row[c] + (A.bias ? A.bias[c] : 0.0f); };
+    float sq = 0.0f, sk = 0.0f;
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = at(c); sq += v * v; }
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = at(nq + c); sk += v * v; }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) { red[0][w] = sq; red[1][w] = sk; }
+    __syncthreads();
+    sq = 0.0f;
+    sk = 0.0f;
+    for (int i = 0; i < nw; ++i) { sq += red[0][i]; sk += red[1][i]; }      // the same order in every thread
+    const float rq = 1.0f / sqrtf(sq / (float)nq + A.eps), rk = 1.0f / sqrtf(sk / (float)nk + A.eps);
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) qbuf[(size_t)t * nq + c] = from_f<T>(at(c) * rq * A.q_norm[c]);
+    if (page < 0 || page >= A.n_pages) {
+        if (threadIdx.x == 0) atomicExch(A.err, 1);
+        return;
+    }
+    T* base = pool + (size_t)page * A.page_elems;
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+        const int g = c / A.d, i = c - g * A.d;
+        base[A.k_off + ((size_t)g * A.page_size + in_pg) * A.d + i] = from_f<T>(at(nq + c) * rk * A.k_norm[c]);
+    }
+    for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+        const int g = c / A.dv, i = c - g * A.dv;
+        base[A.v_off + ((size_t)g * A.page_size + in_pg) * A.dv + i] = from_f<T>(at(nq + nk + c));
     }
 }
 
@@ -639,7 +707,8 @@ constexpr int kAttnWarps = 4;
 constexpr int kAttnMaxV = 16;  // value size up to 512; the kernels are built for 8 (up to 256) and 16 lanes' worth of columns
 
 __device__ __forceinline__ float attn_gate(const AttnArgs& A, size_t t, int h, int c) {
-    return sigmoidf_(A.proj[t * A.n_in + A.gate_off + (size_t)h * A.gate_ld + (size_t)c * A.gate_step]);
+    if (!A.has_gate) return A.out_scale;
+    return A.out_scale * sigmoidf_(A.proj[t * A.n_in + A.gate_off + (size_t)h * A.gate_ld + (size_t)c * A.gate_step]);
 }
 
 template <class T, int MAXV>
@@ -656,12 +725,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
     __syncwarp();
     const int pos = A.tok_pos[t];
     const int32_t* bt = A.block_table + (size_t)A.tok_seq[t] * A.max_pages;
-    const float r1 = A.r1 ? A.r1[h] : 0.0f, r2 = A.r1 ? A.r2[h] : 0.0f;
+    const float r1 = A.r1 ? A.r1[h] : 0.0f, r2 = A.r1 ? A.r2[h] : 0.0f, slope = A.slope ? A.slope[h] : 0.0f;
     float m = A.sink ? A.sink[h] : -INFINITY, l = A.sink ? 1.0f : 0.0f;
     float o[MAXV];
 #pragma unroll
     for (int e = 0; e < MAXV; ++e) o[e] = 0.0f;
-    for (int j0 = 0; j0 <= pos; j0 += 32) {
+    for (int j0 = attn_first_key(A, pos); j0 <= pos; j0 += 32) {
         const int j = j0 + lane;
         float s = -INFINITY;
         const T* vrow = nullptr;
@@ -672,8 +741,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
             vrow = base + A.v_off + ((size_t)g * A.page_size + in_pg) * A.v_ld;
             float dot = 0.0f;
             for (int c = 0; c < A.d; ++c) dot = fmaf(qs[c], to_f<T>(k[c]), dot);
-            s = dot * A.scale;
-            if (A.r1) s -= r1 * log1pf(r2 * (float)(pos - j));
+            s = attn_score<false>(A, dot, pos - j, r1, r2, slope);
         }
         const float mn = fmaxf(m, warp_max(s));          // finite: lane 0 of every round holds a visible key
         const float p = (j <= pos) ? expf(s - mn) : 0.0f;
@@ -697,7 +765,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(const AttnArgs A,
 #pragma unroll
     for (int e = 0; e < MAXV; ++e) {
         const int c = lane + e * 32;
-        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * attn_gate(A, t, h, c));
+        if (c < A.dv) out[(size_t)t * A.out_ld + h * A.dv + c] = from_f<T>(o[e] * inv * attn_gate(A, t, h, c));
     }
 }
 
@@ -750,9 +818,12 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
     const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
     if (n > kShortSeq || r >= n) return;
     const int t = t0 + r, pos = A.tok_pos[t];
-    const int j_lo = blockIdx.z * A.split_len;
-    if (j_lo > pos) return;
-    const int j_hi = min(pos, j_lo + A.split_len - 1);
+    // with a window the ranges are counted from the one that holds the row's first visible key
+    const int j_first = attn_first_key(A, pos);
+    const int range = j_first / A.split_len + blockIdx.z;
+    if (range * A.split_len > pos) return;
+    const int j_lo = max(range * A.split_len, j_first);
+    const int j_hi = min(pos, (range + 1) * A.split_len - 1);
     const int Gq = A.H / A.G, nwarp = blockDim.x >> 5;
     const int groups = (Gq + nwarp - 1) / nwarp;
     const int g = blockIdx.y / groups, hq = (blockIdx.y % groups) * nwarp + (threadIdx.x >> 5);
@@ -766,7 +837,7 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
     T* Vs = A.v_in_k ? Ks : Ks + 32 * ldk;
     const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
     for (int c = lane; c < A.d; c += 32) qs[c] = to_f<T>(qbuf[((size_t)t * A.H + h) * A.d + c]);
-    const float r1 = A.r1 ? A.r1[h] : 0.0f, r2 = A.r1 ? A.r2[h] : 0.0f;
+    const float r1 = A.r1 ? A.r1[h] : 0.0f, r2 = A.r1 ? A.r2[h] : 0.0f, slope = A.slope ? A.slope[h] : 0.0f;
     float m = -INFINITY, l = 0.0f;
     float o[MAXV];
 #pragma unroll
@@ -799,8 +870,7 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs A, const
         const int j = j0 + lane;
         float sc = -INFINITY;
         if (lane < cnt) {
-            sc = key_dot<T>(qs, Ks + lane * ldk, A.d) * A.scale;
-            if (A.r1) sc -= r1 * log1pf(r2 * (float)(pos - j));
+            sc = attn_score<false>(A, key_dot<T>(qs, Ks + lane * ldk, A.d), pos - j, r1, r2, slope);
         }
         const float mn = fmaxf(m, warp_max(sc));          // finite: lane 0 of every round holds a valid key
         const float p = lane < cnt ? expf(sc - mn) : 0.0f;
@@ -842,7 +912,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __
     const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
     if (n > kShortSeq || r >= n) return;
     const int t = t0 + r, pos = A.tok_pos[t];
-    const int ns = pos / A.split_len + 1;
+    const int ns = pos / A.split_len - attn_first_key(A, pos) / A.split_len + 1;
     const float* src = A.part + ((size_t)x * A.H + h) * A.n_splits * (A.dv + 2);
     // lanes take the ranges' maxima and weights side by side; the value columns are then summed range by range with the
     // weights handed on by shuffles, so that no load waits for an earlier one
@@ -878,7 +948,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A, T* __
 #pragma unroll
     for (int e = 0; e < MAXV; ++e) {
         const int c = lane + e * 32;
-        if (c < A.dv) out[((size_t)t * A.H + h) * A.dv + c] = from_f<T>(o[e] * inv * attn_gate(A, t, h, c));
+        if (c < A.dv) out[(size_t)t * A.out_ld + h * A.dv + c] = from_f<T>(o[e] * inv * attn_gate(A, t, h, c));
     }
 }
 
@@ -971,6 +1041,10 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
     const int last_pos = pos0 + min(n, tile * 64 + 64) - 1;
     const bool penalty = A.r1 != nullptr;
     const float r1 = penalty ? A.r1[h] : 0.0f, r2 = penalty ? A.r2[h] : 0.0f, sink = A.sink ? A.sink[h] : -INFINITY;
+    const float slope = A.slope ? A.slope[h] : 0.0f;
+    const int win = A.window > 0 ? A.window : 0x3fffffff;
+    // the first key tile any row of this block sees (tiles are 64 absolute positions)
+    const int j_start = attn_first_key(A, pos0 + tile * 64) / 64 * 64;
     float m_a = sink, m_b = sink, l_a = (tq == 0 && A.sink) ? 1.0f : 0.0f, l_b = l_a;
     float o[DV / 8][4];
 #pragma unroll
@@ -988,9 +1062,9 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
         if (!VK) stage_rows<DV, true>(Vs + buf * kTileV, A.dv, [&](int row) { return row_of(row, A.v_off, A.v_ld); });
         cp_async_commit_group();
     };
-    stage_tile(0, 0);
+    stage_tile(j_start, 0);
     int buf = 0;
-    for (int j0 = 0; j0 <= last_pos; j0 += 64, buf ^= 1) {
+    for (int j0 = j_start; j0 <= last_pos; j0 += 64, buf ^= 1) {
         if (j0 + 64 <= last_pos) {
             stage_tile(j0 + 64, buf ^ 1);
             cp_async_wait_group<1>();
@@ -1000,7 +1074,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
         __syncthreads();
         const bf16* Kt = Ks + buf * kTile;
         const bf16* Vt = Vs + buf * kTileV;
-        if (j0 <= pos0 + tile * 64 + warp * 16 + 15) {          // this warp's rows see at least one key of the tile
+        if (j0 <= pos0 + tile * 64 + warp * 16 + 15 && j0 + 63 > pos0 + tile * 64 + warp * 16 - win) {      // this warp's rows see a key of the tile
             float S[8][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
@@ -1021,7 +1095,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
                 for (int e = 0; e < 4; ++e) {
                     const int j = j0 + nt * 8 + tq * 2 + (e & 1);
                     const int i = e < 2 ? i_a : i_b;
-                    const float v = j <= i ? S[nt][e] * A.scale - (penalty ? r1 * __logf(1.0f + r2 * (float)(i - j)) : 0.0f) : -INFINITY;
+                    const float v = (j <= i && i - j < win) ? attn_score<true>(A, S[nt][e], i - j, r1, r2, slope) : -INFINITY;
                     S[nt][e] = v;
                     if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                 }
@@ -1074,7 +1148,7 @@ __global__ void __launch_bounds__(128) attn_flash_kernel(const AttnArgs A, const
             const int row = e < 2 ? row_a : row_b, c = nt * 8 + tq * 2 + (e & 1);
             if (row < n && c < A.dv) {
                 const size_t t = t0 + row;
-                out[(t * A.H + h) * A.dv + c] = __float2bfloat16_rn(o[nt][e] * (e < 2 ? inv_a : inv_b) * attn_gate(A, t, h, c));
+                out[t * A.out_ld + h * A.dv + c] = __float2bfloat16_rn(o[nt][e] * (e < 2 ? inv_a : inv_b) * attn_gate(A, t, h, c));
             }
         }
 }
@@ -1367,12 +1441,17 @@ struct RunInfo {
     size_t k_off = 0, v_off = 0;   // attention: element offsets inside a page
     size_t state_off = 0;          // recurrent: float offset inside a slot
     size_t freq_off = 0;           // latent attention: float offset of the run's rotation frequencies in the table
+    size_t conv_off = 0;           // state-space: float offset of the convolution's last inputs inside a slot
 };
 
 struct SmolLm {
     SmolLmConfig cfg;
     std::vector<SmolLmLayer> layers;
+    std::vector<SmolLmLayer> sides;       // sides[i]: the mixer beside layer i's (layers[i].side points here, or is null)
     std::vector<RunInfo> runs;
+    std::vector<RunInfo> side_runs;       // the cache / state placement of a run's side mixer
+    size_t o_conv = 0, o_head = 0;        // state-space: convolved channels [T][channels], per-head decay and step [2][T][heads]
+    int max_conv = 0, max_ssd_heads = 0;
     SmolLmGlobals g{};
     size_t page_elems = 0, slot_floats = 0, esize = 2;
     int max_in = 0, max_mix = 0, max_ff = 0, max_hd = 0, max_q = 0;
@@ -1406,11 +1485,16 @@ struct SmolLm {
 static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
 
 static int n_in_of(const SmolLmLayer& L) {
-    if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim + L.heads * L.vdim;
+    if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim + (L.no_gate ? 0 : L.heads * L.vdim);
+    if (L.mixer == SMOL_LM_MIX_STATE_SPACE) return 2 * L.heads * L.vdim + 2 * L.bc_groups * L.n_state + L.heads;
     if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) return L.q_rank + L.kv_rank + L.rot_dim + L.heads;
     if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) return 2 * L.heads * L.dim + 2 * L.heads * L.vdim + L.rank;
     return 5 * L.heads * L.dim + L.rank;
 }
+
+// columns a mixer hands to the output projection
+static int mix_cols_of(const SmolLmLayer& L) { return L.mixer == SMOL_LM_MIX_GENERAL_DELTA ? L.heads * L.dim : L.heads * L.vdim; }
+static bool pairable(const SmolLmLayer& L) { return L.mixer == SMOL_LM_MIX_SINK_ATTENTION || L.mixer == SMOL_LM_MIX_STATE_SPACE; }
 
 extern "C" int smol_lm_abi_version(void) { return SMOL_LM_ABI_VERSION; }
 extern "C" const char* smol_lm_last_error(void) { return g_err.c_str(); }
@@ -1425,16 +1509,21 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     m->cfg = *cfg;
     m->esize = cfg->dtype == SMOL_LM_F32 ? 4 : 2;
     m->layers.assign(layers, layers + cfg->n_layers);
-    for (int n = 0; n < cfg->n_runs; ++n) {
-        const int li = run_layer[n];
-        if (li < 0 || li >= cfg->n_layers) { delete m; return fail(SMOL_ERR_INVALID, "run_layer entry outside the layer array"); }
-        const SmolLmLayer& L = m->layers[li];
-        RunInfo r;
-        r.layer = li;
-        if (L.heads < 1 || L.dim < 1) { delete m; return fail(SMOL_ERR_INVALID, "a layer needs heads >= 1 and dim >= 1"); }
+    m->sides.resize(cfg->n_layers);
+    for (int i = 0; i < cfg->n_layers; ++i)
+        if (m->layers[i].side) {
+            m->sides[i] = *m->layers[i].side;
+            m->sides[i].side = nullptr;
+            m->layers[i].side = &m->sides[i];
+        }
+    // places one mixer's cache or state in the pools and widens the workspace for it; returns 0 or an error code
+    auto place = [&](const SmolLmLayer& L, RunInfo& r) -> int {
+        if (L.heads < 1 || (L.dim < 1 && L.mixer != SMOL_LM_MIX_STATE_SPACE)) return fail(SMOL_ERR_INVALID, "a layer needs heads >= 1 and dim >= 1");
+        if (L.in_bias && !pairable(L)) return fail(SMOL_ERR_UNSUPPORTED, "in_bias: softmax attention and the state-space recurrence only");
         if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) {
-            if (L.kv_heads < 1 || L.heads % L.kv_heads != 0 || L.vdim < 1) { delete m; return fail(SMOL_ERR_INVALID, "attention: heads must be a multiple of kv_heads"); }
-            if (L.vdim > 32 * kAttnMaxV) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "attention: value size above 256"); }
+            if (L.kv_heads < 1 || L.heads % L.kv_heads != 0 || L.vdim < 1) return fail(SMOL_ERR_INVALID, "attention: heads must be a multiple of kv_heads");
+            if (L.vdim > 32 * kAttnMaxV) return fail(SMOL_ERR_UNSUPPORTED, "attention: value size above 256");
+            if (L.window < 0 || L.softcap < 0.0f) return fail(SMOL_ERR_INVALID, "attention: window and softcap must not be negative");
             r.k_off = m->page_elems;
             r.v_off = r.k_off + (size_t)L.kv_heads * cfg->page_size * L.dim;
             m->page_elems = r.v_off + (size_t)L.kv_heads * cfg->page_size * L.vdim;
@@ -1442,19 +1531,32 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_heads = std::max(m->max_heads, L.heads);
             m->max_vdim = std::max(m->max_vdim, L.vdim);
             m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
+        } else if (L.mixer == SMOL_LM_MIX_STATE_SPACE) {
+            if (L.vdim < 1 || L.n_state < 1 || L.bc_groups < 1 || L.heads % L.bc_groups != 0 || L.conv_taps < 1 || L.norm_parts < 1 ||
+                (L.heads * L.vdim) % L.norm_parts != 0)
+                return fail(SMOL_ERR_INVALID, "state-space: heads must be a multiple of bc_groups, heads * vdim of norm_parts");
+            if (L.n_state > 256 || L.conv_taps > kMaxTaps) return fail(SMOL_ERR_UNSUPPORTED, "state-space: state size above 256 or more than 16 taps");
+            const int ch = L.heads * L.vdim + 2 * L.bc_groups * L.n_state;
+            r.state_off = m->slot_floats;
+            m->slot_floats += (size_t)L.heads * L.n_state * L.vdim;
+            r.conv_off = m->slot_floats;
+            m->slot_floats += (size_t)(L.conv_taps - 1) * ch;
+            m->slot_floats = (m->slot_floats + 3) / 4 * 4;          // the next state starts on a 16-byte boundary
+            m->max_hd = std::max(m->max_hd, L.heads * L.vdim);
+            m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
+            m->max_conv = std::max(m->max_conv, ch);
+            m->max_ssd_heads = std::max(m->max_ssd_heads, L.heads);
         } else if (L.mixer == SMOL_LM_MIX_GENERAL_DELTA) {
-            if (L.dim > 256) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256"); }
-            if (L.rank < 1) { delete m; return fail(SMOL_ERR_INVALID, "recurrent mixer: rank must be positive"); }
+            if (L.dim > 256) return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256");
+            if (L.rank < 1) return fail(SMOL_ERR_INVALID, "recurrent mixer: rank must be positive");
             r.state_off = m->slot_floats;
             m->slot_floats += (size_t)L.heads * L.dim * L.dim;
             m->max_hd = std::max(m->max_hd, L.heads * L.dim);
             m->max_mix = std::max(m->max_mix, L.heads * L.dim);
         } else if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) {
-            if (L.vdim < 1 || L.q_rank < 1 || L.kv_rank < 1 || L.rot_dim < 0 || L.rot_dims < 0 || L.rot_dims > L.rot_dim || L.rot_dims % 2) {
-                delete m;
+            if (L.vdim < 1 || L.q_rank < 1 || L.kv_rank < 1 || L.rot_dim < 0 || L.rot_dims < 0 || L.rot_dims > L.rot_dim || L.rot_dims % 2)
                 return fail(SMOL_ERR_INVALID, "latent attention: vdim, q_rank, kv_rank must be positive, rot_dims even and at most rot_dim");
-            }
-            if (L.kv_rank > 32 * kAttnMaxV) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "latent attention: latent size above 512"); }
+            if (L.kv_rank > 32 * kAttnMaxV) return fail(SMOL_ERR_UNSUPPORTED, "latent attention: latent size above 512");
             // a cached position: the latent, then the shared rotated key part; keys and values are the same row
             r.k_off = r.v_off = m->page_elems;
             m->page_elems += (size_t)cfg->page_size * (L.kv_rank + L.rot_dim);
@@ -1468,20 +1570,37 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_cq = std::max(m->max_cq, L.q_rank);
             m->max_qf = std::max(m->max_qf, L.heads * (L.dim + L.rot_dim));
         } else if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) {
-            if (L.dim > 256) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256"); }
-            if (L.rank < 1 || L.vdim < 1 || !(L.decay_tau > 0.0f)) { delete m; return fail(SMOL_ERR_INVALID, "gated linear: rank, vdim, tau must be positive"); }
+            if (L.dim > 256) return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256");
+            if (L.rank < 1 || L.vdim < 1 || !(L.decay_tau > 0.0f)) return fail(SMOL_ERR_INVALID, "gated linear: rank, vdim, tau must be positive");
             r.state_off = m->slot_floats;
             m->slot_floats += (size_t)L.heads * L.dim * L.vdim;
             m->max_hd = std::max(m->max_hd, L.heads * std::max(L.dim, L.vdim));
             m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
         } else {
-            delete m;
             return fail(SMOL_ERR_UNSUPPORTED, "unknown mixer kind");
         }
+        return SMOL_OK;
+    };
+    for (int n = 0; n < cfg->n_runs; ++n) {
+        const int li = run_layer[n];
+        if (li < 0 || li >= cfg->n_layers) { delete m; return fail(SMOL_ERR_INVALID, "run_layer entry outside the layer array"); }
+        const SmolLmLayer& L = m->layers[li];
+        RunInfo r, rs;
+        r.layer = rs.layer = li;
+        int rc = place(L, r);
+        if (rc == SMOL_OK && L.side) {
+            if (!pairable(L) || !pairable(*L.side)) rc = fail(SMOL_ERR_UNSUPPORTED, "mixers side by side: softmax attention and the state-space recurrence only");
+            else if (cfg->block == SMOL_LM_BLOCK_POSTNORM) rc = fail(SMOL_ERR_UNSUPPORTED, "mixers side by side need the sandwich block");
+            else rc = place(*L.side, rs);
+            if (rc == SMOL_OK) m->max_mix = std::max(m->max_mix, mix_cols_of(L) + mix_cols_of(*L.side));
+        }
+        if (rc == SMOL_OK && cfg->block == SMOL_LM_BLOCK_POSTNORM && (L.out_bias || L.route_input))
+            rc = fail(SMOL_ERR_UNSUPPORTED, "out_bias and route_input need the sandwich block");
+        if (rc != SMOL_OK) { delete m; return rc; }
         if (L.mlp < SMOL_LM_MLP_NONE || L.mlp > SMOL_LM_MLP_EXPERTS) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "unknown feed-forward kind"); }
         if (L.mlp == SMOL_LM_MLP_POLYNORM) m->max_ff = std::max(m->max_ff, L.ff);
         if (L.mlp == SMOL_LM_MLP_GATED || L.mlp == SMOL_LM_MLP_EXPERTS) {
-            if (L.ff < 1 || (L.mlp_act != SMOL_LM_ACT_GELU_TANH && L.mlp_act != SMOL_LM_ACT_SILU)) { delete m; return fail(SMOL_ERR_INVALID, "gated feed-forward: ff and activation"); }
+            if (L.ff < 1 || L.mlp_act < SMOL_LM_ACT_GELU_TANH || L.mlp_act > SMOL_LM_ACT_CLAMPED) { delete m; return fail(SMOL_ERR_INVALID, "gated feed-forward: ff and activation"); }
         }
         if (L.mlp == SMOL_LM_MLP_GATED) m->max_ff = std::max(m->max_ff, 2 * L.ff);
         if (L.mlp == SMOL_LM_MLP_EXPERTS) {
@@ -1496,8 +1615,9 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_experts = std::max(m->max_experts, L.n_experts);
             m->max_pair_ff = std::max(m->max_pair_ff, L.top_k * L.ff);
         }
-        m->max_in = std::max(m->max_in, n_in_of(L));
+        m->max_in = std::max(m->max_in, n_in_of(L) + (L.side ? n_in_of(*L.side) : 0));
         m->runs.push_back(r);
+        m->side_runs.push_back(rs);
     }
     // pages hold 16-byte aligned rows whatever the sizes
     m->page_elems = (m->page_elems + 7) / 8 * 8;
@@ -1529,6 +1649,10 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
         m->o_cq = carve(T * (size_t)m->max_cq * E);
         m->o_qf = carve(T * (size_t)m->max_qf * 4);
         m->o_freq = carve(m->freq_table.size() * 4 + 4);
+    }
+    if (m->max_conv > 0) {
+        m->o_conv = carve(T * (size_t)m->max_conv * 4);
+        m->o_head = carve(2 * T * (size_t)m->max_ssd_heads * 4);
     }
     if (m->max_top > 0) {
         const size_t pairs = T * (size_t)m->max_top;
@@ -1562,7 +1686,8 @@ extern "C" int32_t* smol_lm_error_word(SmolLm* m) { return (m && m->bound) ? rei
 template <int DK>
 static cudaError_t scan_attribute() {
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * delta_buf_floats(DK) * sizeof(float)));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gla_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * gla_buf_floats(DK) * sizeof(float)));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gla_scan_kernel<DK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * gla_buf_floats(DK) * sizeof(float)));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gla_scan_kernel<DK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * gla_buf_floats(DK) * sizeof(float)));
     return e;
 }
 static constexpr int flash_smem_bytes(int DK, int DV, bool vk) { return 2 * 64 * ((DK + 8) + (vk ? 0 : DV + 8)) * (int)sizeof(bf16); }
@@ -1738,8 +1863,17 @@ template <int DK>
 static cudaError_t launch_gla_scan(const GlaArgs& A, int n_seqs, const float* dec, float* pool, float* o_raw, cudaStream_t st) {
     constexpr int CB = delta_block_cols(DK), threads = CB * delta_lanes(DK);
     const int groups = (A.dv + CB - 1) / CB;
-    gla_scan_kernel<DK><<<n_seqs * A.H * groups, threads, 2 * gla_buf_floats(DK) * sizeof(float), st>>>(A, dec, pool, o_raw);
+    if (A.head_decay) gla_scan_kernel<DK, true><<<n_seqs * A.H * groups, threads, 2 * gla_buf_floats(DK) * sizeof(float), st>>>(A, dec, pool, o_raw);
+    else gla_scan_kernel<DK, false><<<n_seqs * A.H * groups, threads, 2 * gla_buf_floats(DK) * sizeof(float), st>>>(A, dec, pool, o_raw);
     return cudaGetLastError();
+}
+// the scan over key sizes up to 256: the smallest built size that holds A.d
+static cudaError_t launch_gla_scan_any(const GlaArgs& A, int n_seqs, const float* dec, float* pool, float* o_raw, cudaStream_t st) {
+    if (A.d <= 16) return launch_gla_scan<16>(A, n_seqs, dec, pool, o_raw, st);
+    if (A.d <= 32) return launch_gla_scan<32>(A, n_seqs, dec, pool, o_raw, st);
+    if (A.d <= 64) return launch_gla_scan<64>(A, n_seqs, dec, pool, o_raw, st);
+    if (A.d <= 128) return launch_gla_scan<128>(A, n_seqs, dec, pool, o_raw, st);
+    return launch_gla_scan<256>(A, n_seqs, dec, pool, o_raw, st);
 }
 
 // The attention kernels over the rows of a step: prompt portions on the tensor-core form (bf16, `flash`) or the
@@ -1756,6 +1890,7 @@ static void launch_attention(SmolLm* m, const SmolLmStep* s, AttnArgs& A, bool f
     const int max_n = s->max_seq_tokens > 0 ? s->max_seq_tokens : Tn;
     const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, c.max_context - 1) : c.max_context - 1;
     A.n_splits = std::min(m->max_splits, (max_pos / m->split_len + 4) / 4 * 4);
+    if (A.window > 0) A.n_splits = std::min(A.n_splits, ((A.window - 1) / m->split_len + 2 + 3) / 4 * 4);      // ranges a window can touch
     if (max_n > kShortSeq) {
         if (flash) {
             dim3 grid((max_n + 63) / 64, s->n_seqs, A.H);
@@ -1815,43 +1950,108 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
     const bool postnorm = c.block == SMOL_LM_BLOCK_POSTNORM;
     const size_t hist_stride = (size_t)Tn * D;
     constexpr bool kIsF32 = sizeof(T) == 4;
+    const float woff = c.norm_plain ? 0.0f : 1.0f;
+    float* conv = reinterpret_cast<float*>(m->ws + m->o_conv);
+    float* head = reinterpret_cast<float*>(m->ws + m->o_head);
     auto cast_grid = [](size_t n) { return (int)std::min<size_t>((n + 255) / 256, 148 * 8); };
 
     if (postnorm) {
         embed_gain_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), D, c.vocab, m->g.embed_norm, c.norm_eps, x, hist, hn);
     } else {
         embed_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), c.embed_scale, D, c.vocab,
-                                                  m->layers[m->runs[0].layer].norm1, c.norm_eps, x, hn);
+                                                  m->layers[m->runs[0].layer].norm1, c.norm_eps, x, hn, woff);
     }
     m->launches++;
     for (size_t n = 0; n < m->runs.size(); ++n) {
         const RunInfo& R = m->runs[n];
         const SmolLmLayer& L = m->layers[R.layer];
-        const int n_in = n_in_of(L);
+        const int n_in_main = n_in_of(L), n_in = n_in_main + (L.side ? n_in_of(*L.side) : 0);
         CU(linear<T>(m, hn, static_cast<const T*>(L.w_in), proj, Tn, n_in, D, st));
+        const int mix_ld = mix_cols_of(L) + (L.side ? mix_cols_of(*L.side) : 0);      // row stride of the mixers' shared result
         int mix_cols;
         const T* mix_in = mix;          // what the output projection reads
-        if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION || L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) {
+        // Softmax attention over keys and values in the paged pool.  pj / bias: this mixer's rows of the fused projection.
+        auto attention = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj, const float* bias, T* mix_at) -> int {
             AttnArgs A;
-            A.proj = proj; A.n_in = n_in;
+            A.proj = pj; A.n_in = n_in; A.bias = bias;
+            A.tok_seq = s->tok_seq; A.tok_pos = s->tok_pos; A.block_table = s->block_table;
+            A.max_pages = s->max_pages; A.page_size = c.page_size; A.n_pages = m->n_pages;
+            A.page_elems = m->page_elems; A.k_off = Ri.k_off; A.v_off = Ri.v_off;
+            A.H = M.heads; A.scale = M.score_scale; A.eps = c.norm_eps;
+            A.n_tokens = Tn; A.err = err;
+            A.G = M.kv_heads; A.d = M.dim; A.dv = M.vdim;
+            A.k_ld = M.dim; A.v_ld = M.vdim; A.v_in_k = 0;
+            A.gate_off = (size_t)M.heads * M.dim + (size_t)M.kv_heads * (M.dim + M.vdim); A.gate_ld = M.vdim; A.gate_step = 1;
+            A.has_gate = M.no_gate ? 0 : 1;
+            A.q_norm = M.q_norm; A.k_norm = M.k_norm; A.r1 = M.dist_r1; A.r2 = M.dist_r2; A.sink = M.sink;
+            A.slope = M.dist_slope; A.window = M.window; A.softcap = M.softcap;
+            A.out_ld = mix_ld; A.out_scale = M.mix_scale != 0.0f ? M.mix_scale : 1.0f;
+            if (M.norm_whole) {
+                attn_prep_whole_kernel<T><<<Tn, 128, 0, st>>>(A, qbuf, pool);
+            } else {
+                const int units = Tn * (M.heads + 2 * M.kv_heads);
+                attn_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(A, qbuf, pool);
+            }
+            m->launches += 1;
+            const bool flash = sizeof(T) == 2 && std::max(M.dim, M.vdim) <= 128;
+            if (M.vdim <= 256) launch_attention<T, 8>(m, s, A, flash, qbuf, pool, mix_at, st);
+            else launch_attention<T, 16>(m, s, A, flash, qbuf, pool, mix_at, st);
+            return SMOL_OK;
+        };
+        // State-space recurrence: convolution and per-head step / decay, the scan over the slot's state, the slot's new
+        // convolution inputs, then skip, gate and the grouped norm.
+        auto state_space = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj, const float* bias, T* mix_at) -> int {
+            const int inner = M.heads * M.vdim, gn = M.bc_groups * M.n_state, ch = inner + 2 * gn;
+            SsdArgs P;
+            P.proj = pj; P.bias = bias; P.n_in = n_in; P.H = M.heads; P.dv = M.vdim; P.N = M.n_state; P.G = M.bc_groups;
+            P.taps = M.conv_taps; P.parts = M.norm_parts; P.n_tokens = Tn; P.eps = c.norm_eps;
+            P.conv_w = M.conv_w; P.conv_b = M.conv_b; P.dt_bias = M.dt_bias; P.a_log = M.a_log; P.skip = M.skip; P.out_norm = M.out_norm;
+            P.seq_start = s->seq_start; P.seq_pos0 = s->seq_pos0; P.seq_slot = s->seq_slot; P.tok_seq = s->tok_seq;
+            P.slot_floats = m->slot_floats; P.conv_off = Ri.conv_off; P.n_slots = m->n_slots; P.err = err;
+            P.out_ld = mix_ld; P.out_scale = M.mix_scale != 0.0f ? M.mix_scale : 1.0f;
+            const dim3 cgrid(Tn, (std::max(ch, M.heads) + 127) / 128);
+            ssd_conv_kernel<<<cgrid, 128, 0, st>>>(P, m->slots, conv, head);
+            GlaArgs A;
+            A.proj = pj; A.n_in = n_in; A.H = M.heads; A.d = M.n_state; A.dv = M.vdim; A.rank = 0; A.n_tokens = Tn;
+            A.q_scale = 1.0f; A.tau = 1.0f; A.eps = c.norm_eps;
+            A.decay_w2 = A.decay_bias = A.out_norm = nullptr;
+            A.seq_start = s->seq_start; A.seq_pos0 = s->seq_pos0; A.seq_slot = s->seq_slot;
+            A.slot_floats = m->slot_floats; A.state_off = Ri.state_off; A.n_slots = m->n_slots; A.err = err;
+            A.q_src = conv + inner + gn; A.k_src = conv + inner; A.v_src = conv;
+            A.q_ld = A.k_ld = A.v_ld = ch;
+            A.qk_share = M.heads / M.bc_groups;
+            A.head_decay = head; A.head_step = head + (size_t)Tn * M.heads;
+            A.out_ld = mix_ld; A.out_scale = 1.0f;
+            CU(launch_gla_scan_any(A, s->n_seqs, nullptr, m->slots, oraw, st));
+            if (M.conv_taps > 1) {
+                ssd_conv_state_kernel<<<dim3(s->n_seqs, (ch + 127) / 128), 128, 0, st>>>(P, m->slots);
+                m->launches += 1;
+            }
+            ssd_out_kernel<T><<<dim3(Tn, M.norm_parts), 256, 0, st>>>(P, oraw, conv, mix_at);
+            m->launches += 3;
+            return SMOL_OK;
+        };
+        if (pairable(L)) {
+            int rc = L.mixer == SMOL_LM_MIX_SINK_ATTENTION ? attention(L, R, proj, L.in_bias, mix) : state_space(L, R, proj, L.in_bias, mix);
+            if (rc == SMOL_OK && L.side) {
+                const SmolLmLayer& S = *L.side;
+                const float* sb = L.in_bias ? L.in_bias + n_in_main : nullptr;
+                T* at = mix + mix_cols_of(L);
+                rc = S.mixer == SMOL_LM_MIX_SINK_ATTENTION ? attention(S, m->side_runs[n], proj + n_in_main, sb, at)
+                                                           : state_space(S, m->side_runs[n], proj + n_in_main, sb, at);
+            }
+            if (rc != SMOL_OK) return rc;
+            mix_cols = mix_ld;
+        } else if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) {
+            AttnArgs A;
+            A.proj = proj; A.n_in = n_in; A.bias = nullptr;
             A.tok_seq = s->tok_seq; A.tok_pos = s->tok_pos; A.block_table = s->block_table;
             A.max_pages = s->max_pages; A.page_size = c.page_size; A.n_pages = m->n_pages;
             A.page_elems = m->page_elems; A.k_off = R.k_off; A.v_off = R.v_off;
             A.H = L.heads; A.scale = L.score_scale; A.eps = c.norm_eps;
             A.n_tokens = Tn; A.err = err;
-            if (L.mixer == SMOL_LM_MIX_SINK_ATTENTION) {
-                A.G = L.kv_heads; A.d = L.dim; A.dv = L.vdim;
-                A.k_ld = L.dim; A.v_ld = L.vdim; A.v_in_k = 0;
-                A.gate_off = (size_t)L.heads * L.dim + (size_t)L.kv_heads * (L.dim + L.vdim); A.gate_ld = L.vdim; A.gate_step = 1;
-                A.q_norm = L.q_norm; A.k_norm = L.k_norm; A.r1 = L.dist_r1; A.r2 = L.dist_r2; A.sink = L.sink;
-                const int units = Tn * (L.heads + 2 * L.kv_heads);
-                attn_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(A, qbuf, pool);
-                m->launches += 1;
-                const bool flash = sizeof(T) == 2 && std::max(L.dim, L.vdim) <= 128;
-                if (L.vdim <= 256) launch_attention<T, 8>(m, s, A, flash, qbuf, pool, mix, st);
-                else launch_attention<T, 16>(m, s, A, flash, qbuf, pool, mix, st);
-                mix_cols = L.heads * L.vdim;
-            } else {
+            A.slope = nullptr; A.window = 0; A.softcap = 0.0f; A.has_gate = 1; A.out_scale = 1.0f; A.out_ld = L.heads * L.kv_rank;
+            {
                 const int dk = L.kv_rank + L.rot_dim, qw = L.dim + L.rot_dim;
                 T* cq = reinterpret_cast<T*>(m->ws + m->o_cq);
                 float* qf = reinterpret_cast<float*>(m->ws + m->o_qf);
@@ -1898,14 +2098,9 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.decay_w2 = L.decay_w2; A.decay_bias = L.decay_bias; A.out_norm = L.out_norm;
             A.seq_start = s->seq_start; A.seq_pos0 = s->seq_pos0; A.seq_slot = s->seq_slot;
             A.slot_floats = m->slot_floats; A.state_off = R.state_off; A.n_slots = m->n_slots; A.err = err;
+            gla_sources_from_proj(A);
             gla_prep_kernel<<<dim3(Tn, (L.heads * L.dim + 127) / 128), 128, L.rank * sizeof(float), st>>>(A, dec);
-            cudaError_t e;
-            if (L.dim <= 16) e = launch_gla_scan<16>(A, s->n_seqs, dec, m->slots, oraw, st);
-            else if (L.dim <= 32) e = launch_gla_scan<32>(A, s->n_seqs, dec, m->slots, oraw, st);
-            else if (L.dim <= 64) e = launch_gla_scan<64>(A, s->n_seqs, dec, m->slots, oraw, st);
-            else if (L.dim <= 128) e = launch_gla_scan<128>(A, s->n_seqs, dec, m->slots, oraw, st);
-            else e = launch_gla_scan<256>(A, s->n_seqs, dec, m->slots, oraw, st);
-            CU(e);
+            CU(launch_gla_scan_any(A, s->n_seqs, dec, m->slots, oraw, st));
             gla_out_kernel<T><<<(Tn * L.heads + 3) / 4, 128, 0, st>>>(A, oraw, mix);
             m->launches += 3;
             mix_cols = L.heads * L.vdim;
@@ -1935,6 +2130,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
         RoutedSum routed;
         routed.yp = nullptr; routed.slot_of = nullptr; routed.sel_w = nullptr; routed.top = 0;
         const RoutedSum no_sum = routed;
+        auto actp_of = [](const SmolLmLayer& M) { return ActParams{M.mlp_act, M.act_limit, M.act_alpha}; };
         auto feed_forward = [&]() -> int {
             if (L.mlp == SMOL_LM_MLP_POLYNORM) {
                 CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, L.ff, D, st));
@@ -1943,7 +2139,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 m->launches += 1;
             } else if (L.mlp == SMOL_LM_MLP_GATED) {
                 CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, 2 * L.ff, D, st));
-                gated_act_kernel<T><<<cast_grid((size_t)Tn * L.ff / 4), 256, 0, st>>>(z, L.ff, L.mlp_act, (size_t)Tn, act);
+                gated_act_kernel<T><<<cast_grid((size_t)Tn * L.ff / 4), 256, 0, st>>>(z, L.ff, actp_of(L), (size_t)Tn, act);
                 CU(linear<T>(m, act, static_cast<const T*>(L.w_down), y, Tn, D, L.ff, st));
                 m->launches += 1;
             } else if (L.mlp == SMOL_LM_MLP_EXPERTS) {
@@ -1961,6 +2157,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 RouteArgs Rt;
                 Rt.w_router = L.w_router; Rt.bias = L.route_bias; Rt.D = D; Rt.E = L.n_experts + L.n_identity; Rt.E_real = L.n_experts;
                 Rt.top = L.top_k; Rt.n_groups = L.n_groups; Rt.keep = L.keep_groups; Rt.scale = L.router_scale; Rt.n_tokens = Tn;
+                Rt.score = L.router_score; Rt.plain = L.router_plain;
                 const int pairs = Tn * L.top_k;
                 // the router reads the sublayer's input in fp32 where the block keeps it (post-norm), else its T form
                 float* r_logits = reinterpret_cast<float*>(m->ws + m->o_rlogits);
@@ -1985,30 +2182,37 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                     io2.sw = (long long)D * L.ff;
                     io2.tile_group = tile_g; io2.tile_row0 = tile_r; io2.seg = seg; io2.n_tiles = n_tiles;
                     const size_t act_n = (size_t)pairs * L.ff;
+                    // a router whose weight multiplies the expert's input: the rows are copied into sorted order, each times
+                    // its weight, and the products read that copy
+                    T* ap = reinterpret_cast<T*>(m->ws + m->o_ap);
+                    if (L.route_input) {
+                        moe_gather_scaled_kernel<T><<<pairs, 128, 0, st>>>(hn, perm, L.top_k, sel_w, seg + L.n_experts, D, ap);
+                        m->launches++;
+                    }
                     if (few) {
-                        moe_gemv_kernel<-1><<<dim3((2 * L.ff + 7) / 8, pairs), 256, 0, st>>>(hn, perm, L.top_k, sel_id, seg + L.n_experts,
-                                                                                            reinterpret_cast<const bf16*>(L.w_experts_in), io.sw, zp, 2 * L.ff, D);
+                        moe_gemv_kernel<false><<<dim3((2 * L.ff + 7) / 8, pairs), 256, 0, st>>>(L.route_input ? ap : hn, perm, L.route_input ? 0 : L.top_k, sel_id,
+                                                                                               seg + L.n_experts, reinterpret_cast<const bf16*>(L.w_experts_in), io.sw,
+                                                                                               zp, 2 * L.ff, D, actp_of(L));
                         // the second product applies the activation as it reads the first one's result
-                        if (L.mlp_act == SMOL_LM_ACT_SILU)
-                            moe_gemv_kernel<SMOL_LM_ACT_SILU><<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(zp, perm, 0, sel_id, seg + L.n_experts,
-                                                                                                        reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff);
-                        else
-                            moe_gemv_kernel<SMOL_LM_ACT_GELU_TANH><<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(zp, perm, 0, sel_id, seg + L.n_experts,
-                                                                                                             reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff);
+                        moe_gemv_kernel<true><<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(zp, perm, 0, sel_id, seg + L.n_experts,
+                                                                                        reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff, actp_of(L));
                         m->launches += 1;
                     } else {
                         bool done = false;
                         if (big) {
-                            bf16* ap = reinterpret_cast<bf16*>(m->ws + m->o_ap);
-                            moe_gather_kernel<<<pairs, 128, 0, st>>>(reinterpret_cast<const bf16*>(hn), perm, L.top_k, seg + L.n_experts, D, ap);
-                            m->launches++;
-                            done = linear_grouped_tc(m, ap, reinterpret_cast<const bf16*>(L.w_experts_in), zp, pairs, L.n_experts, 2 * L.ff, D, io, st);
+                            if (!L.route_input) {
+                                moe_gather_kernel<<<pairs, 128, 0, st>>>(reinterpret_cast<const bf16*>(hn), perm, L.top_k, seg + L.n_experts, D,
+                                                                         reinterpret_cast<bf16*>(ap));
+                                m->launches++;
+                            }
+                            done = linear_grouped_tc(m, reinterpret_cast<const bf16*>(ap), reinterpret_cast<const bf16*>(L.w_experts_in), zp, pairs, L.n_experts,
+                                                     2 * L.ff, D, io, st);
                         }
                         if (!done) {
-                            io.gather = perm; io.gather_div = L.top_k;
-                            CU(linear_ex<T>(m, hn, static_cast<const T*>(L.w_experts_in), zp, pairs, 2 * L.ff, D, io, 1, tiles, st));
+                            if (!L.route_input) { io.gather = perm; io.gather_div = L.top_k; }
+                            CU(linear_ex<T>(m, L.route_input ? ap : hn, static_cast<const T*>(L.w_experts_in), zp, pairs, 2 * L.ff, D, io, 1, tiles, st));
                         }
-                        gated_act_kernel<T><<<cast_grid(act_n / 4), 256, 0, st>>>(zp, L.ff, L.mlp_act, (size_t)pairs, actp);
+                        gated_act_kernel<T><<<cast_grid(act_n / 4), 256, 0, st>>>(zp, L.ff, actp_of(L), (size_t)pairs, actp);
                         if (!(big && linear_grouped_tc(m, reinterpret_cast<const bf16*>(actp), reinterpret_cast<const bf16*>(L.w_experts_out), yp, pairs,
                                                        L.n_experts, D, L.ff, io2, st)))
                             CU(linear_ex<T>(m, actp, static_cast<const T*>(L.w_experts_out), yp, pairs, D, L.ff, io2, 1, tiles, st));
@@ -2020,7 +2224,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 if (postnorm) {
                     routed.yp = yp; routed.slot_of = slot_of; routed.sel_w = sel_w; routed.top = L.top_k;      // summed by the norm that follows
                 } else {
-                    moe_combine_kernel<T><<<Tn, nthr, 0, st>>>(hn, yp, slot_of, sel_w, L.top_k, D, y);
+                    moe_combine_kernel<T><<<Tn, nthr, 0, st>>>(hn, yp, slot_of, L.route_input ? nullptr : sel_w, L.top_k, D, y);
                     m->launches += 1;
                 }
             }
@@ -2041,13 +2245,13 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 m->launches += 1;
             }
         } else if (L.mlp != SMOL_LM_MLP_NONE) {
-            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, L.norm2, c.norm_eps, D, hn);
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, L.norm2, c.norm_eps, D, hn, woff, L.out_bias);
             const int rc = feed_forward();
             if (rc != SMOL_OK) return rc;
-            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm2b, L.ls2, next_norm1, c.norm_eps, D, hn);
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm2b, L.ls2, next_norm1, c.norm_eps, D, hn, woff, nullptr);
             m->launches += 2;
         } else {
-            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, next_norm1, c.norm_eps, D, hn);
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, next_norm1, c.norm_eps, D, hn, woff, L.out_bias);
             m->launches += 1;
         }
         if (s->trace) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));
@@ -2055,7 +2259,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
     if (s->n_want > 0) {
         if (postnorm) post_norm_kernel<T><<<s->n_want, nthr, 2 * D * sizeof(float), st>>>(x, nullptr, c.logit_scale, m->g.final_norm, c.norm_eps, D, nullptr, 0, 0,
                                                                                       nullptr, s->want_rows, hw, RoutedSum{nullptr, nullptr, nullptr, 0});
-        else norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw);
+        else norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw, woff);
         m->launches++;
         CU(linear<T>(m, hw, static_cast<const T*>(m->g.head), s->logits, s->n_want, c.vocab, D, st));
         if (!postnorm && c.logit_scale != 1.0f) {

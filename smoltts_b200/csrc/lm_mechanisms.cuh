@@ -3,7 +3,10 @@
 //     depth-weighted average of all earlier layer results,
 //   - latent attention (queries through a latent; one cached latent + one rotated shared key part per position),
 //   - the gated linear recurrence (decay per key channel, state [dim, vdim] per head in the sequence's slot),
-//   - gated feed-forwards and the routed mixture of experts (grouped choice, identity outputs).
+//   - the state-space recurrence (short causal convolution, one decay per head and step; it shares the scan with the gated
+//     linear recurrence),
+//   - gated feed-forwards and the routed mixture of experts (grouped choice, identity outputs; softmax or sigmoid scores,
+//     weights on the experts' outputs or inputs).
 // Everything here is fp32 except what is written for a matrix product (T).
 #pragma once
 
@@ -15,6 +18,21 @@ __device__ __forceinline__ float gelu_tanh_(float z) {
 }
 __device__ __forceinline__ float silu_(float z) { return z * sigmoidf_(z); }
 __device__ __forceinline__ float gated_act_(int kind, float z) { return kind == SMOL_LM_ACT_SILU ? silu_(z) : gelu_tanh_(z); }
+// A gated unit's value from its gate and up inputs.  SMOL_LM_ACT_CLAMPED: g = min(gate, limit), u = clamp(up, -limit, limit),
+// g * sigmoid(alpha * g) * (u + 1); the other kinds: act(gate) * up.
+struct ActParams {
+    int kind;
+    float limit, alpha;
+};
+__device__ __forceinline__ float gated_unit_(const ActParams& a, float g, float u) {
+    if (a.kind == SMOL_LM_ACT_CLAMPED) {
+        g = fminf(g, a.limit);
+        u = fminf(fmaxf(u, -a.limit), a.limit);
+        return g * sigmoidf_(a.alpha * g) * (u + 1.0f);
+    }
+    return gated_act_(a.kind, g) * u;
+}
+__device__ __forceinline__ float softplus_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 // ln(sigmoid(z)) without overflow: -(max(-z, 0) + ln(1 + exp(-|z|)))
 __device__ __forceinline__ float log_sigmoid_(float z) { return -(fmaxf(-z, 0.0f) + log1pf(expf(-fabsf(z)))); }
 
@@ -296,7 +314,24 @@ struct GlaArgs {
     size_t slot_floats, state_off;
     int n_slots;
     int32_t* err;
+    // Where the scan reads a token's vectors: head h takes q_src[t * q_ld + (h / qk_share) * d + i], k likewise (qk_share
+    // heads share one query / key vector), v_src[t * v_ld + h * dv + j].  The gated linear recurrence reads them from proj.
+    const float *q_src, *k_src, *v_src;
+    int q_ld, k_ld, v_ld, qk_share;
+    // SCALAR form of the scan: one decay per (token, head) head_decay[t * H + h] instead of one per key channel, and the
+    // value is multiplied by head_step[t * H + h] as it enters the state.
+    const float *head_decay, *head_step;
+    int out_ld;                                        // row stride of the finished mixer output
+    float out_scale;
 };
+__host__ __device__ inline void gla_sources_from_proj(GlaArgs& A) {
+    A.q_src = A.proj; A.k_src = A.proj + A.H * A.d; A.v_src = A.proj + 2 * A.H * A.d;
+    A.q_ld = A.k_ld = A.v_ld = A.n_in;
+    A.qk_share = 1;
+    A.head_decay = A.head_step = nullptr;
+    A.out_ld = A.H * A.dv;
+    A.out_scale = 1.0f;
+}
 
 // decay[t][c] for the H*d key channels; blockIdx.y: a slice of blockDim.x channels
 __global__ void gla_prep_kernel(const GlaArgs A, float* __restrict__ decay) {
@@ -317,27 +352,34 @@ __global__ void gla_prep_kernel(const GlaArgs A, float* __restrict__ decay) {
 // L adjacent lanes share a column, lane q keeping the key rows 4*(e*L + q) .. +3 of it in registers (DK >= d rows; rows
 // beyond d see zero keys and queries).  q, k, w of the head and v of the block's columns come into shared memory
 // kDeltaChunk tokens at a time by cp.async, the next chunk while the current one is computed.
-__host__ __device__ constexpr int gla_buf_floats(int DK) { return kDeltaChunk * (3 * DK + delta_block_cols(DK)); }
+// a buffer: q | k | w as [chunk][DK] each, v [chunk][CB], then the scalar form's decay and step [chunk] each
+__host__ __device__ constexpr int gla_buf_floats(int DK) { return kDeltaChunk * (3 * DK + delta_block_cols(DK) + 2); }
 
-template <int DK, int VEC>
+template <int DK, int VEC, bool SCALAR>
 __device__ __forceinline__ void gla_stage(const GlaArgs& A, float* buf, int c0, int n, int h, int j0, int nc, const float* decay) {
     constexpr int CB = delta_block_cols(DK), PL = kDeltaChunk * DK;
-    const int d = A.d, HD = A.H * d, dq = d / VEC, ncq = (nc + VEC - 1) / VEC;
+    const int d = A.d, HD = A.H * d, dq = d / VEC, ncq = (nc + VEC - 1) / VEC, hs = h / A.qk_share;
     for (int idx = threadIdx.x; idx < n * dq; idx += blockDim.x) {
         const int tt = idx / dq, i = (idx - tt * dq) * VEC;
-        const float* prow = A.proj + (size_t)(c0 + tt) * A.n_in + h * d + i;
         float* dst = buf + tt * DK + i;
-        cp_async_f<VEC>(dst, prow);                                             // q
-        cp_async_f<VEC>(dst + PL, prow + HD);                                   // k
-        cp_async_f<VEC>(dst + 2 * PL, decay + (size_t)(c0 + tt) * HD + h * d + i);
+        cp_async_f<VEC>(dst, A.q_src + (size_t)(c0 + tt) * A.q_ld + hs * d + i);
+        cp_async_f<VEC>(dst + PL, A.k_src + (size_t)(c0 + tt) * A.k_ld + hs * d + i);
+        if (!SCALAR) cp_async_f<VEC>(dst + 2 * PL, decay + (size_t)(c0 + tt) * HD + h * d + i);
     }
     for (int idx = threadIdx.x; idx < n * ncq; idx += blockDim.x) {
         const int tt = idx / ncq, j = (idx - tt * ncq) * VEC;
-        cp_async_f<VEC>(buf + 3 * PL + tt * CB + j, A.proj + (size_t)(c0 + tt) * A.n_in + 2 * HD + h * A.dv + j0 + j);
+        cp_async_f<VEC>(buf + 3 * PL + tt * CB + j, A.v_src + (size_t)(c0 + tt) * A.v_ld + h * A.dv + j0 + j);
+    }
+    if (SCALAR) {
+        float* sc = buf + 3 * PL + kDeltaChunk * CB;
+        for (int tt = threadIdx.x; tt < n; tt += blockDim.x) {
+            cp_async_f<1>(sc + tt, A.head_decay + (size_t)(c0 + tt) * A.H + h);
+            cp_async_f<1>(sc + kDeltaChunk + tt, A.head_step + (size_t)(c0 + tt) * A.H + h);
+        }
     }
 }
 
-template <int DK>
+template <int DK, bool SCALAR>
 __global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) gla_scan_kernel(const GlaArgs A, const float* __restrict__ decay,
                                                                                          float* __restrict__ state_pool,
                                                                                          float* __restrict__ o_raw) {
@@ -357,12 +399,13 @@ __global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) gla_sc
         if (threadIdx.x == 0) atomicExch(A.err, 2);
         return;
     }
-    // 16-byte copies need every source to start on a 16-byte boundary: d, dv and the row length multiples of 4
-    const bool vec = (d % 4 == 0) && (dv % 4 == 0) && (A.n_in % 4 == 0);
+    // 16-byte copies need every source to start on a 16-byte boundary: d, dv and the row lengths multiples of 4
+    const bool vec = (d % 4 == 0) && (dv % 4 == 0) && (A.q_ld % 4 == 0) && (A.k_ld % 4 == 0) && (A.v_ld % 4 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(A.q_src) | reinterpret_cast<uintptr_t>(A.k_src) | reinterpret_cast<uintptr_t>(A.v_src)) % 16 == 0);
     for (int i = threadIdx.x; i < 2 * kBuf; i += blockDim.x) sh[i] = 0.0f;      // padded channels and columns stay zero for good
     __syncthreads();
-    if (vec) gla_stage<DK, 4>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay);
-    else gla_stage<DK, 1>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay);
+    if (vec) gla_stage<DK, 4, SCALAR>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay);
+    else gla_stage<DK, 1, SCALAR>(A, sh, t0, min(kDeltaChunk, t1 - t0), h, j0, nc, decay);
     cp_async_commit();
     float* st = state_pool + (size_t)slot * A.slot_floats + A.state_off + (size_t)h * d * dv;
     float S[RV][4];
@@ -381,13 +424,14 @@ __global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) gla_sc
         __syncthreads();                          // this chunk has landed; every thread is done with the other buffer
         if (c0 + kDeltaChunk < t1) {
             const int nn = min(kDeltaChunk, t1 - c0 - kDeltaChunk);
-            if (vec) gla_stage<DK, 4>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay);
-            else gla_stage<DK, 1>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay);
+            if (vec) gla_stage<DK, 4, SCALAR>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay);
+            else gla_stage<DK, 1, SCALAR>(A, sh + (cur ^ 1) * kBuf, c0 + kDeltaChunk, nn, h, j0, nc, decay);
             cp_async_commit();
         }
         const float* b = sh + cur * kBuf;
         const float4* s4 = reinterpret_cast<const float4*>(b) + q;      // piece e of a vector of token tt: s4[(tt*DK)/4 + e*L]
         const float* s_v = b + 3 * PL + col;
+        const float* s_sc = b + 3 * PL + kDeltaChunk * CB;      // scalar form: decay [chunk], step [chunk]
         // four tokens at a time: their state updates follow one another, their sums over the key rows are then reduced side
         // by side, so that the shuffle latency is paid once per four tokens
         for (int tt = 0; tt < n; tt += 4) {
@@ -396,12 +440,13 @@ __global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) gla_sc
             for (int u = 0; u < 4; ++u) {
                 po[u] = 0.0f;
                 if (tt + u < n) {
-                    const float v = s_v[(tt + u) * CB];
+                    const float v = SCALAR ? s_v[(tt + u) * CB] * s_sc[kDeltaChunk + tt + u] : s_v[(tt + u) * CB];
+                    const float w1 = SCALAR ? s_sc[tt + u] : 0.0f;
                     float sa = 0.0f, sb = 0.0f;
 #pragma unroll
                     for (int e = 0; e < RV; ++e) {
                         const float4* p = s4 + (tt + u) * (DK / 4) + e * L;
-                        const float4 qv = p[0], kv = p[PL / 4], wv = p[2 * (PL / 4)];
+                        const float4 qv = p[0], kv = p[PL / 4], wv = SCALAR ? make_float4(w1, w1, w1, w1) : p[2 * (PL / 4)];
                         S[e][0] = fmaf(wv.x, S[e][0], kv.x * v);
                         S[e][1] = fmaf(wv.y, S[e][1], kv.y * v);
                         S[e][2] = fmaf(wv.z, S[e][2], kv.z * v);
@@ -448,27 +493,127 @@ __global__ void gla_out_kernel(const GlaArgs A, const float* __restrict__ o_raw,
     for (int c = lane; c < dv; c += 32) ss = fmaf(o[c], o[c], ss);
     ss = warp_sum(ss);
     const float rs = 1.0f / sqrtf(ss / (float)dv + A.eps);
-    for (int c = lane; c < dv; c += 32) out[(size_t)t * HV + h * dv + c] = from_f<T>(o[c] * rs * A.out_norm[c] * silu_(gate[c]));
+    for (int c = lane; c < dv; c += 32) out[(size_t)t * A.out_ld + h * dv + c] = from_f<T>(o[c] * rs * A.out_norm[c] * silu_(gate[c]) * A.out_scale);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Gated feed-forward: z rows hold gate [F] | up [F]; out = act(gate) * up in T.
+// State-space recurrence.  proj row layout: gate z [H*dv] | x [H*dv] | B [G*N] | C [G*N] | dt [H]; N = d of the scan's
+// arguments (the state of a head is [N, dv]), G groups of H / G heads share B and C.  The x | B | C channels pass a causal
+// convolution over the sequence's positions (taps inputs, the last tap on the current token, zeros before position 0)
+// and silu.  The convolution's last taps - 1 inputs live in the sequence's slot behind the states.
+struct SsdArgs {
+    const float* proj;        // this mixer's rows of the fused projection
+    const float* bias;        // of those rows, or nullptr
+    int n_in, H, dv, N, G, taps, parts, n_tokens;
+    float eps;
+    const float *conv_w, *conv_b, *dt_bias, *a_log, *skip, *out_norm;
+    const int32_t *seq_start, *seq_pos0, *seq_slot, *tok_seq;
+    size_t slot_floats, conv_off;      // float offset of this run's convolution inputs inside a slot: [taps - 1][channels]
+    int n_slots;
+    int32_t* err;
+    int out_ld;
+    float out_scale;
+};
+
+// Blocks (token, slice of channels): conv[t][c] = silu(b[c] + sum_k w[c][k] * in[pos - (taps-1) + k][c]); an input of an
+// earlier step comes from the slot, one before the sequence's start is zero.  The block of a token's first slice also
+// leaves the heads' step dt = softplus(dt + bias) and decay exp(-exp(a_log) * dt) in `head` ([T][H] decay, then [T][H] step).
+__global__ void ssd_conv_kernel(const SsdArgs A, const float* __restrict__ slots, float* __restrict__ conv, float* __restrict__ head) {
+    const int t = blockIdx.x, inner = A.H * A.dv, ch = inner + 2 * A.G * A.N;
+    const int s = A.tok_seq[t], t0 = A.seq_start[s], pos0 = A.seq_pos0[s];
+    const int r = t - t0;                      // the token's place in this step's portion
+    const int slot = A.seq_slot[s];
+    if (slot < 0 || slot >= A.n_slots) {
+        if (threadIdx.x == 0) atomicExch(A.err, 2);
+        return;
+    }
+    const float* before = slots + (size_t)slot * A.slot_floats + A.conv_off;      // inputs of positions pos0 - (taps-1) .. pos0 - 1
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c < ch) {
+        float acc = A.conv_b[c];
+        const float bc = A.bias ? A.bias[inner + c] : 0.0f;
+        for (int k = 0; k < A.taps; ++k) {
+            const int back = A.taps - 1 - k;       // how many positions before the token
+            float v = 0.0f;
+            if (back <= r) v = A.proj[(size_t)(t - back) * A.n_in + inner + c] + bc;
+            else if (pos0 + r - back >= 0) v = before[(size_t)(A.taps - 1 - (back - r)) * ch + c];
+            acc = fmaf(A.conv_w[(size_t)c * A.taps + k], v, acc);
+        }
+        conv[(size_t)t * ch + c] = silu_(acc);
+    }
+    if (blockIdx.y == 0 && threadIdx.x < A.H) {
+        const int h = threadIdx.x;
+        const float raw = A.proj[(size_t)t * A.n_in + inner + ch + h] + (A.bias ? A.bias[inner + ch + h] : 0.0f);
+        const float dt = softplus_(raw + A.dt_bias[h]);
+        head[(size_t)t * A.H + h] = expf(-expf(A.a_log[h]) * dt);
+        head[(size_t)(A.n_tokens + t) * A.H + h] = dt;
+    }
+}
+
+// After the convolution of a step: the slot keeps the last taps - 1 inputs of every sequence.  Blocks (sequence, slice of
+// channels); a thread reads all it needs of the old inputs before it writes.
+constexpr int kMaxTaps = 16;
+__global__ void ssd_conv_state_kernel(const SsdArgs A, float* __restrict__ slots) {
+    const int s = blockIdx.x, inner = A.H * A.dv, ch = inner + 2 * A.G * A.N, keep = A.taps - 1;
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0, pos0 = A.seq_pos0[s];
+    const int slot = A.seq_slot[s];
+    if (slot < 0 || slot >= A.n_slots) return;
+    float* st = slots + (size_t)slot * A.slot_floats + A.conv_off;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= ch) return;
+    const float bc = A.bias ? A.bias[inner + c] : 0.0f;
+    float nv[kMaxTaps];
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) {
+        if (k >= keep) break;
+        const int back = keep - k;                 // new entry k is the input `back` positions before the next token
+        if (back <= n) nv[k] = A.proj[(size_t)(t0 + n - back) * A.n_in + inner + c] + bc;
+        else nv[k] = (pos0 + n - back >= 0) ? st[(size_t)(keep - (back - n)) * ch + c] : 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) {
+        if (k >= keep) break;
+        st[(size_t)k * ch + c] = nv[k];
+    }
+}
+
+// End of the mixer: y = o + skip_h * x, times silu(z), divided by the root mean square of its part (the H*dv channels form
+// `parts` equal parts), times out_norm, times out_scale, written in T.  Blocks (token, part).
 template <class T>
-__global__ void gated_act_kernel(const float* __restrict__ z, int F, int kind, size_t rows, T* __restrict__ out) {
+__global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw, const float* __restrict__ conv, T* __restrict__ out) {
+    __shared__ float red[33];
+    const int t = blockIdx.x, inner = A.H * A.dv, ch = inner + 2 * A.G * A.N, len = inner / A.parts;
+    const int c0 = blockIdx.y * len;
+    const float* z = A.proj + (size_t)t * A.n_in;
+    auto value = [&](int c) {
+        const float zz = z[c] + (A.bias ? A.bias[c] : 0.0f);
+        return (o_raw[(size_t)t * inner + c] + A.skip[c / A.dv] * conv[(size_t)t * ch + c]) * silu_(zz);
+    };
+    float ss = 0.0f;
+    for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) { const float v = value(c); ss += v * v; }
+    ss = block_sum(ss, red);
+    const float r = A.out_scale / sqrtf(ss / (float)len + A.eps);
+    for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) out[(size_t)t * A.out_ld + c] = from_f<T>(value(c) * r * A.out_norm[c]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Gated feed-forward: z rows hold gate [F] | up [F]; out = the gated unit's value (act(gate) * up, or the clamped form) in T.
+template <class T>
+__global__ void gated_act_kernel(const float* __restrict__ z, int F, const ActParams kind, size_t rows, T* __restrict__ out) {
     if (F % 4 == 0) {                      // 16-byte pieces
         const size_t n = rows * (F / 4);
         for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
             const size_t r = i / (F / 4), c = (i - r * (F / 4)) * 4;
             const float4 g = *reinterpret_cast<const float4*>(z + r * 2 * F + c), u = *reinterpret_cast<const float4*>(z + r * 2 * F + F + c);
-            store4<T>(out + r * F + c, gated_act_(kind, g.x) * u.x, gated_act_(kind, g.y) * u.y, gated_act_(kind, g.z) * u.z,
-                      gated_act_(kind, g.w) * u.w);
+            store4<T>(out + r * F + c, gated_unit_(kind, g.x, u.x), gated_unit_(kind, g.y, u.y), gated_unit_(kind, g.z, u.z),
+                      gated_unit_(kind, g.w, u.w));
         }
         return;
     }
     const size_t n = rows * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / F, c = i - r * F;
-        out[i] = from_f<T>(gated_act_(kind, z[r * 2 * F + c]) * z[r * 2 * F + F + c]);
+        out[i] = from_f<T>(gated_unit_(kind, z[r * 2 * F + c], z[r * 2 * F + F + c]));
     }
 }
 
@@ -479,13 +624,15 @@ struct RouteArgs {
     int D, E, E_real, top, n_groups, keep;
     float scale;
     int n_tokens;
+    int score;        // SMOL_LM_ROUTE_*: softmax over the outputs, or a sigmoid of each
+    int plain;        // 1: a chosen output's weight is its score (times scale), not divided by the chosen scores' sum
 };
 constexpr int kMaxRouted = 1024;       // router outputs (experts + identity outputs)
 constexpr int kMaxTop = 32;
 
 // Blocks (token, group of 4 router outputs): one warp per output takes the fp32 dot product of the token's input and the
 // output's router row and leaves it in `logits`.  The block that finishes a token last (a counter per token, which it
-// sets back to zero) then chooses: softmax scores s, choice scores s + bias; outputs outside the `keep` best groups (a
+// sets back to zero) then chooses: scores s (softmax or sigmoid), choice scores s + bias (bias == nullptr: none); outputs outside the `keep` best groups (a
 // group's score: its best choice score) cannot be chosen; the `top` best choice scores are chosen (ties: the lower
 // index; the choices are kept in that order), their weights are the scores s over their sum, times `scale`.  Ranks are
 // counted, not sorted: output e is chosen if fewer than `top` allowed outputs beat it.
@@ -539,12 +686,14 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const
     mx = red[0];
     for (int w = 1; w < nw; ++w) mx = fmaxf(mx, red[w]);
     float sum = 0.0f;
-    for (int e = threadIdx.x; e < A.E; e += blockDim.x) sum += expf(s[e] - mx);
-    sum = block_sum(sum, red);
+    if (A.score == SMOL_LM_ROUTE_SOFTMAX) {
+        for (int e = threadIdx.x; e < A.E; e += blockDim.x) sum += expf(s[e] - mx);
+        sum = block_sum(sum, red);
+    }
     for (int e = threadIdx.x; e < A.E; e += blockDim.x) {
-        const float p = expf(s[e] - mx) / sum;
+        const float p = A.score == SMOL_LM_ROUTE_SOFTMAX ? expf(s[e] - mx) / sum : sigmoidf_(s[e]);
         s[e] = p;
-        choice[e] = p + A.bias[e];
+        choice[e] = p + (A.bias ? A.bias[e] : 0.0f);
     }
     __syncthreads();
     const int size = A.E / A.n_groups;
@@ -579,7 +728,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const
     if (threadIdx.x < A.top) {
         float den = 0.0f;
         for (int k = 0; k < A.top; ++k) den += top_s[k];
-        sel_w[(size_t)t * A.top + threadIdx.x] = top_s[threadIdx.x] / (den + 1e-20f) * A.scale;
+        sel_w[(size_t)t * A.top + threadIdx.x] = A.plain ? top_s[threadIdx.x] * A.scale : top_s[threadIdx.x] / (den + 1e-20f) * A.scale;
     }
 }
 
@@ -641,16 +790,31 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int32_t* __r
     }
 }
 
+// The same copy for routers whose weight multiplies the expert's INPUT: row r is weight[pair] * (the pair's input row),
+// the product taken in fp32 and rounded to T once.
+template <class T>
+__global__ void moe_gather_scaled_kernel(const T* __restrict__ h, const int32_t* __restrict__ perm, int div, const float* __restrict__ sel_w,
+                                         const int32_t* __restrict__ n_sorted, int D, T* __restrict__ out) {
+    const int r = blockIdx.x;
+    if (r >= *n_sorted) return;
+    const int pair = perm[r];
+    const float w = sel_w[pair];
+    const T* src = h + (size_t)(pair / div) * D;
+    T* dst = out + (size_t)r * D;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = from_f<T>(w * to_f<T>(src[c]));
+}
+
 // The grouped product for a handful of rows (decoding): one warp per (sorted row, output column), lanes cut K into 16-byte
 // pieces, the expert's weight row is streamed once.  Sorted row r belongs to pair perm[r], whose router output names the
 // expert; it reads a's row perm[r] / gather_div (gather_div == 0: row r itself).  Needs K % 8 == 0 and 16-byte aligned rows.
-// ACT >= 0: a is instead the fp32 result of the first product [rows][2 K] (gate | up), and the row is act(gate) * up, rounded
-// to bf16 as the tile forms round it.
+// ACT: a is instead the fp32 result of the first product [rows][2 K] (gate | up), and the row is the gated unit's value,
+// rounded to bf16 as the tile forms round it.
 constexpr int kMoeGemvPairs = 32;
-template <int ACT>
+template <bool ACT>
 __global__ void __launch_bounds__(256) moe_gemv_kernel(const void* __restrict__ a_any, const int32_t* __restrict__ perm, int gather_div,
                                                        const int32_t* __restrict__ sel_id, const int32_t* __restrict__ n_sorted,
-                                                       const bf16* __restrict__ w, long long w_stride, float* __restrict__ y, int N, int K) {
+                                                       const bf16* __restrict__ w, long long w_stride, float* __restrict__ y, int N, int K,
+                                                       const ActParams act) {
     const int r = blockIdx.y;
     if (r >= *n_sorted) return;
     const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -658,16 +822,16 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const void* __restrict__ 
     const int pair = perm[r];
     const bf16* wr = w + (long long)sel_id[pair] * w_stride + (size_t)n * K;
     float acc = 0.0f;
-    if (ACT >= 0) {
+    if (ACT) {
         const float* zr = static_cast<const float*>(a_any) + (size_t)r * 2 * K;
         for (int k = lane * 8; k < K; k += 256) {
             const uint4 wv = ldg_stream(wr + k);
             const float4 g0 = *reinterpret_cast<const float4*>(zr + k), g1 = *reinterpret_cast<const float4*>(zr + k + 4);
             const float4 u0 = *reinterpret_cast<const float4*>(zr + K + k), u1 = *reinterpret_cast<const float4*>(zr + K + k + 4);
-            acc = fmaf(bf16_round(gated_act_(ACT, g0.x) * u0.x), bf_lo(wv.x), acc); acc = fmaf(bf16_round(gated_act_(ACT, g0.y) * u0.y), bf_hi(wv.x), acc);
-            acc = fmaf(bf16_round(gated_act_(ACT, g0.z) * u0.z), bf_lo(wv.y), acc); acc = fmaf(bf16_round(gated_act_(ACT, g0.w) * u0.w), bf_hi(wv.y), acc);
-            acc = fmaf(bf16_round(gated_act_(ACT, g1.x) * u1.x), bf_lo(wv.z), acc); acc = fmaf(bf16_round(gated_act_(ACT, g1.y) * u1.y), bf_hi(wv.z), acc);
-            acc = fmaf(bf16_round(gated_act_(ACT, g1.z) * u1.z), bf_lo(wv.w), acc); acc = fmaf(bf16_round(gated_act_(ACT, g1.w) * u1.w), bf_hi(wv.w), acc);
+            acc = fmaf(bf16_round(gated_unit_(act, g0.x, u0.x)), bf_lo(wv.x), acc); acc = fmaf(bf16_round(gated_unit_(act, g0.y, u0.y)), bf_hi(wv.x), acc);
+            acc = fmaf(bf16_round(gated_unit_(act, g0.z, u0.z)), bf_lo(wv.y), acc); acc = fmaf(bf16_round(gated_unit_(act, g0.w, u0.w)), bf_hi(wv.y), acc);
+            acc = fmaf(bf16_round(gated_unit_(act, g1.x, u1.x)), bf_lo(wv.z), acc); acc = fmaf(bf16_round(gated_unit_(act, g1.y, u1.y)), bf_hi(wv.z), acc);
+            acc = fmaf(bf16_round(gated_unit_(act, g1.z, u1.z)), bf_lo(wv.w), acc); acc = fmaf(bf16_round(gated_unit_(act, g1.w, u1.w)), bf_hi(wv.w), acc);
         }
         acc = warp_sum(acc);
         if (lane == 0) y[(size_t)r * N + n] = acc;
@@ -686,6 +850,7 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const void* __restrict__ 
 }
 
 // y[t] = sum_k w[t][k] * (expert output of pair (t, k), or the input x[t] for an identity output), k ascending.
+// sel_w == nullptr: every weight is 1 (the weights went into the experts' inputs).
 template <class TI>
 __global__ void moe_combine_kernel(const TI* __restrict__ x, const float* __restrict__ yp, const int32_t* __restrict__ slot_of,
                                    const float* __restrict__ sel_w, int top, int D, float* __restrict__ y) {
@@ -695,7 +860,7 @@ __global__ void moe_combine_kernel(const TI* __restrict__ x, const float* __rest
         for (int k = 0; k < top; ++k) {
             const int slot = slot_of[(size_t)t * top + k];
             const float v = slot >= 0 ? yp[(size_t)slot * D + c] : to_f<TI>(x[(size_t)t * D + c]);
-            acc = fmaf(sel_w[(size_t)t * top + k], v, acc);
+            acc = fmaf(sel_w ? sel_w[(size_t)t * top + k] : 1.0f, v, acc);
         }
         y[(size_t)t * D + c] = acc;
     }

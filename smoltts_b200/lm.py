@@ -7,6 +7,9 @@ per-sequence slot), with PolyNorm feed-forwards, pre- and post-norms around ever
 ``MaferaxLM`` serves the Maferax design: post-norm layers with one gain per norm and a depth-weighted average of all
 earlier layer results; latent attention (one cached latent and one rotated shared key part per position, in the paged
 pool) or a gated linear recurrence (state per head in the slot); gated feed-forwards or a routed mixture of experts.
+``SunutarLM`` serves the Sunutar design: sandwich layers whose mixer is a pair on the same input -- windowed attention
+(keys and values in the paged pool) beside a state-space recurrence (state and convolution inputs in the slot) -- with
+clamped gated feed-forwards, dense or routed by sigmoid scores; the logits reuse the embedding table.
 
 The engine owns two pools -- key/value pages (``PagePool``) and state slots (``SlotPool``) -- and one step function,
 ``forward``: any number of sequences, each with its next tokens (a portion of a prompt or a single decoded token).
@@ -27,8 +30,8 @@ import torch
 
 from . import _capi_lm
 from ._errors import SMOL_ERR_CAPACITY, SmolError
-from .lm_config import (ACT_GELU_TANH, ACT_SILU, BLOCK_POSTNORM, BLOCK_SANDWICH, MAFERAX_MLP_KINDS, MIXER_KINDS, MLP_KINDS,
-                        MaferaxConfig, PamasunConfig)
+from .lm_config import (ACT_CLAMPED, ACT_GELU_TANH, ACT_SILU, BLOCK_POSTNORM, BLOCK_SANDWICH, MAFERAX_MLP_KINDS, MIXER_KINDS, MLP_KINDS,
+                        ROUTE_SIGMOID, MaferaxConfig, PamasunConfig, SunutarConfig)
 from .pool import PagePool, SlotPool
 
 _ST_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "I32": torch.int32, "I64": torch.int64}
@@ -412,3 +415,56 @@ class MaferaxLM(HybridLM):
                 c.w_router, c.route_bias = vec(p + "mlp.router").data_ptr(), vec(p + "mlp.correction").data_ptr()
         return {"config": {"block": BLOCK_POSTNORM, "residual_alpha": cfg.postln_alpha, "logit_scale": cfg.logit_scale},
                 "globals": {"embed": mat("embed"), "head": mat("head"), "final_norm": vec("final.norm"), "embed_norm": vec("embed.norm")}}
+
+
+class SunutarLM(HybridLM):
+    """B200 engine of one Sunutar checkpoint."""
+
+    architecture = "Sunutar"
+    config_class = SunutarConfig
+
+    def _shapes(self, sd):
+        return self.config.tensor_shapes()
+
+    def _describe(self, sd, layers, mat, vec):
+        cfg, D = self.config, self.config.width
+        self._sides = []                                   # the side mixers' structs live as long as the engine's create call needs them
+        residual = vec(torch.full((D,), cfg.residual_mult, dtype=torch.float32))
+        for i, L in enumerate(cfg.layers):
+            p, a, r, c = f"l{i}.", L.left, L.right, layers[i]
+            q = p + "mix.left."
+            # the attention is the layer's own mixer, the recurrence its side mixer: one input product, one output product
+            c.mixer, c.heads, c.kv_heads, c.dim, c.vdim = MIXER_KINDS["attention"], a.heads, a.kv_heads, a.dim, a.vdim
+            c.score_scale, c.window, c.softcap, c.norm_whole, c.no_gate, c.mix_scale = a.scale, a.window, a.softcap, 1, 1, L.left_scale
+            c.q_norm, c.k_norm = vec(q + "q.norm").data_ptr(), vec(q + "k.norm").data_ptr()
+            c.dist_slope = vec(torch.tensor(a.slopes(), dtype=torch.float32)).data_ptr()
+            c.sink = vec(torch.full((a.heads,), a.sink_logit, dtype=torch.float32)).data_ptr()
+            t = p + "mix.right."
+            c.w_in = mat(q + "q", q + "k", q + "v", t + "in").data_ptr()
+            c.in_bias = vec(torch.cat([sd[q + "q.b"].float(), sd[q + "k.b"].float(), sd[q + "v.b"].float(), torch.zeros(r.n_in)])).data_ptr()
+            c.w_out = mat(torch.cat([sd[q + "o"].float(), sd[t + "o"].float()], 1)).data_ptr()
+            c.out_bias = vec(sd[q + "o.b"].float() * L.left_scale).data_ptr()
+            side = _capi_lm.SmolLmLayer()
+            side.mixer, side.heads, side.vdim, side.n_state, side.bc_groups = MIXER_KINDS["state_space"], r.heads, r.vdim, r.state, r.groups
+            side.conv_taps, side.norm_parts, side.mix_scale = r.conv, r.norm_groups, L.right_scale
+            side.conv_w, side.conv_b = vec(t + "conv").data_ptr(), vec(t + "conv.b").data_ptr()
+            side.dt_bias, side.a_log, side.skip = vec(t + "dt_bias").data_ptr(), vec(t + "A_log").data_ptr(), vec(t + "D").data_ptr()
+            side.out_norm = vec(t + "norm").data_ptr()
+            self._sides.append(side)
+            c.side = C.pointer(side)
+            c.norm1, c.norm1b = vec(p + "norm1").data_ptr(), vec(p + "norm1b").data_ptr()
+            c.ls1 = c.ls2 = residual.data_ptr()
+            if L.mlp_kind:
+                c.norm2, c.norm2b = vec(p + "norm2").data_ptr(), vec(p + "norm2b").data_ptr()
+                c.ff, c.mlp_act, c.act_limit, c.act_alpha = L.ff, ACT_CLAMPED, L.limit, cfg.act_alpha
+            c.mlp = MAFERAX_MLP_KINDS[L.mlp_kind]          # none / gated / routed experts
+            if L.mlp_kind == "dense":
+                c.w_up, c.w_down = mat(p + "mlp.gate", p + "mlp.up").data_ptr(), mat(p + "mlp.down").data_ptr()
+            elif L.mlp_kind == "moe":
+                c.n_experts, c.n_identity, c.top_k, c.n_groups, c.keep_groups, c.router_scale = L.experts, 0, L.top, 1, 1, 1.0
+                c.router_score, c.router_plain, c.route_input = ROUTE_SIGMOID, 1, 1
+                c.w_experts_in = mat(*[f"{p}mlp.e{e}.{nm}" for e in range(L.experts) for nm in ("gate", "up")]).data_ptr()
+                c.w_experts_out = mat(*[f"{p}mlp.e{e}.down" for e in range(L.experts)]).data_ptr()
+                c.w_router = vec(p + "mlp.router").data_ptr()
+        embed = mat("embed")
+        return {"config": {"norm_plain": 1}, "globals": {"embed": embed, "head": embed, "final_norm": vec("final.norm")}}

@@ -14,11 +14,12 @@ from pathlib import Path
 from typing import Any, Dict, List, Optional
 
 # values of SMOL_LM_MIX_* (include/smoltts_b200_lm.h)
-MIXER_KINDS = {"attention": 0, "general_delta": 1, "latent_attention": 2, "gla": 3}
+MIXER_KINDS = {"attention": 0, "general_delta": 1, "latent_attention": 2, "gla": 3, "state_space": 4}
 MLP_KINDS = {None: 0, "dense": 1}                        # SMOL_LM_MLP_* of Pamasun: "dense" = up, PolyNorm, down
 # SMOL_LM_MLP_* of Maferax: "dense" = gated (tanh-form gelu), "moe" = routed mixture of gated (silu) experts
 MAFERAX_MLP_KINDS = {None: 0, "dense": 2, "moe": 3}
-ACT_GELU_TANH, ACT_SILU = 0, 1                           # SMOL_LM_ACT_*
+ACT_GELU_TANH, ACT_SILU, ACT_CLAMPED = 0, 1, 2           # SMOL_LM_ACT_*
+ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1                      # SMOL_LM_ROUTE_*
 BLOCK_SANDWICH, BLOCK_POSTNORM = 0, 1                    # SMOL_LM_BLOCK_*
 
 
@@ -350,3 +351,202 @@ class MaferaxConfig:
 
     def matmul_flops_per_token(self, rank: int = 16) -> int:
         return 2 * self.weight_elements(rank, active_only=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Sunutar: sandwich layers with plain norm weights and one residual multiplier; every mixer is a pair that reads the
+# same input -- windowed softmax attention (biases, query/key norm over the whole projection, soft-capped scores, a
+# linear distance penalty, a unit term in the softmax denominator) beside a state-space recurrence (short causal
+# convolution, one decay per head and step) -- summed with two scales; feed-forwards are clamped gated units, dense or
+# routed by sigmoid scores that multiply the experts' inputs.  The logits come from the embedding table.
+
+
+@dataclass
+class WindowAttentionSpec:
+    kind = "attention"
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    window: int           # a query at i sees keys 0 <= i - j < window
+    scale: float
+    softcap: float
+    # fixed by the design (parameters of the kernels): head h's distance slope is 2^(-slope_octaves (h + 1) / heads); the
+    # softmax denominator holds one extra term exp(sink_logit)
+    slope_octaves: float = 8.0
+    sink_logit: float = 0.0
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "WindowAttentionSpec":
+        spec = cls(int(d["heads"]), int(d["kv_heads"]), int(d["dim"]), int(d["vdim"]), int(d["mask"]["size"]), float(d["scale"]), float(d["softcap"]))
+        if spec.heads % spec.kv_heads or spec.window < 1:
+            raise ValueError("attention: heads must be a multiple of kv_heads and the window at least 1")
+        return spec
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "mask": {"size": self.window},
+                "scale": self.scale, "softcap": self.softcap}
+
+    def slopes(self) -> List[float]:
+        return [2.0 ** (-self.slope_octaves * (h + 1) / self.heads) for h in range(self.heads)]
+
+
+@dataclass
+class StateSpaceSpec:
+    kind = "state_space"
+    heads: int
+    vdim: int
+    state: int            # rows of a head's state
+    groups: int           # groups of heads that share the B and C vectors
+    conv: int             # taps of the causal convolution
+    norm_groups: int      # equal parts of the heads * vdim channels, each divided by its own root mean square
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "StateSpaceSpec":
+        spec = cls(int(d["heads"]), int(d["vdim"]), int(d["state"]), int(d["groups"]), int(d["conv"]), int(d["norm_groups"]))
+        if spec.heads % spec.groups or (spec.heads * spec.vdim) % spec.norm_groups or spec.conv < 1:
+            raise ValueError("state space: heads must be a multiple of groups, heads * vdim of norm_groups, conv at least 1")
+        return spec
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "vdim": self.vdim, "state": self.state, "groups": self.groups, "conv": self.conv,
+                "norm_groups": self.norm_groups}
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def channels(self) -> int:
+        """Channels that pass the convolution: x | B | C."""
+        return self.inner + 2 * self.groups * self.state
+
+    @property
+    def n_in(self) -> int:
+        return self.inner + self.channels + self.heads
+
+
+@dataclass
+class SunutarLayer:
+    left: WindowAttentionSpec
+    right: StateSpaceSpec
+    left_scale: float
+    right_scale: float
+    mlp_kind: Optional[str] = None           # None | "dense" | "moe"
+    ff: int = 0                              # dense: feed-forward size; moe: size of one expert
+    limit: float = 0.0                       # clamp of the gated unit
+    experts: int = 0
+    top: int = 0
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "SunutarLayer":
+        if d["type"] != "parallel":
+            raise ValueError(f"unknown mixer type {d['type']!r}; have ['parallel']")
+        m = d["mixer"]
+        L = cls(WindowAttentionSpec.from_dict(m["left"]), StateSpaceSpec.from_dict(m["right"]), float(m["left_scale"]), float(m["right_scale"]))
+        mlp = d.get("mlp")
+        if not mlp:
+            return L
+        if mlp["kind"] == "dense":
+            L.mlp_kind, L.ff, L.limit = "dense", int(mlp["ff"]), float(mlp["limit"])
+        elif mlp["kind"] == "moe":
+            L.mlp_kind, L.ff, L.limit = "moe", int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
+            L.experts, L.top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
+            if not 1 <= L.top <= L.experts:
+                raise ValueError("router: top must lie between 1 and the number of experts")
+        else:
+            raise ValueError(f"unknown feed-forward kind {mlp['kind']!r}")
+        return L
+
+    def to_dict(self) -> Dict[str, Any]:
+        mlp = None
+        if self.mlp_kind == "dense":
+            mlp = {"kind": "dense", "ff": self.ff, "limit": self.limit}
+        elif self.mlp_kind == "moe":
+            mlp = {"kind": "moe", "expert": {"ff": self.ff, "limit": self.limit}, "router": {"experts": self.experts, "top": self.top}}
+        return {"type": "parallel", "mixer": {"left": self.left.to_dict(), "right": self.right.to_dict(), "left_scale": self.left_scale,
+                                              "right_scale": self.right_scale}, "mlp": mlp}
+
+
+@dataclass
+class SunutarConfig:
+    architecture: str = "Sunutar"
+    vocab: int = 0
+    width: int = 0
+    norm_eps: float = 1e-6
+    residual_mult: float = 1.0
+    layers: List[SunutarLayer] = field(default_factory=list)
+    extra: Dict[str, Any] = field(default_factory=dict, repr=False)
+    act_alpha = 1.702             # fixed by the design: the gated unit is g * sigmoid(act_alpha * g) * (u + 1)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "SunutarConfig":
+        known = {"architecture", "vocab", "width", "norm", "residual_mult", "layers"}
+        return cls(architecture=d.get("architecture", "Sunutar"), vocab=int(d["vocab"]), width=int(d["width"]), norm_eps=float(d["norm"]["eps"]),
+                   residual_mult=float(d["residual_mult"]), layers=[SunutarLayer.from_dict(x) for x in d["layers"]],
+                   extra={k: v for k, v in d.items() if k not in known})
+
+    @classmethod
+    def from_pretrained(cls, pathname: str) -> "SunutarConfig":
+        path = Path(pathname)
+        if path.is_dir():
+            path = path / "config.json"
+        with open(path, "r", encoding="utf-8") as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = dict(self.extra)
+        d.update(architecture=self.architecture, vocab=self.vocab, width=self.width, norm={"eps": self.norm_eps},
+                 residual_mult=self.residual_mult, layers=[x.to_dict() for x in self.layers])
+        return d
+
+    def save(self, path: str) -> None:
+        with open(path, "w") as f:
+            json.dump(self.to_dict(), f, indent=1, sort_keys=True)
+
+    def layer_runs(self) -> List[int]:
+        return list(range(len(self.layers)))
+
+    def tensor_shapes(self) -> Dict[str, tuple]:
+        """Checkpoint tensor names and shapes (the logits reuse ``embed``)."""
+        D, V = self.width, self.vocab
+        out: Dict[str, tuple] = {"embed": (V, D), "final.norm": (D,)}
+        for i, L in enumerate(self.layers):
+            p, a, r = f"l{i}.", L.left, L.right
+            for nm in ("norm1", "norm1b"):
+                out[p + nm] = (D,)
+            q = p + "mix.left."
+            nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+            out.update({q + "q": (nq, D), q + "q.b": (nq,), q + "k": (nk, D), q + "k.b": (nk,), q + "v": (nv, D), q + "v.b": (nv,),
+                        q + "q.norm": (nq,), q + "k.norm": (nk,), q + "o": (D, a.heads * a.vdim), q + "o.b": (D,)})
+            q = p + "mix.right."
+            out.update({q + "in": (r.n_in, D), q + "conv": (r.channels, r.conv), q + "conv.b": (r.channels,), q + "dt_bias": (r.heads,),
+                        q + "A_log": (r.heads,), q + "D": (r.heads,), q + "norm": (r.inner,), q + "o": (D, r.inner)})
+            if L.mlp_kind:
+                for nm in ("norm2", "norm2b"):
+                    out[p + nm] = (D,)
+            if L.mlp_kind == "dense":
+                out.update({p + "mlp.gate": (L.ff, D), p + "mlp.up": (L.ff, D), p + "mlp.down": (D, L.ff)})
+            elif L.mlp_kind == "moe":
+                for e in range(L.experts):
+                    out.update({f"{p}mlp.e{e}.gate": (L.ff, D), f"{p}mlp.e{e}.up": (L.ff, D), f"{p}mlp.e{e}.down": (D, L.ff)})
+                out[p + "mlp.router"] = (L.experts, D)
+        return out
+
+    # ---- accounting used by the benchmark ----
+    def weight_elements(self, active_only: bool = False) -> int:
+        """Matrix elements of the model (the embedding table counts once, as the logits' matrix); ``active_only``: those one
+        token touches (``top`` experts)."""
+        total = 0
+        for k, s in self.tensor_shapes().items():
+            if len(s) != 2 or ".conv" in k:
+                continue
+            n = s[0] * s[1]
+            if active_only and ".mlp.e" in k:
+                L = self.layers[int(k[1:k.index(".")])]
+                n = n * L.top / max(L.experts, 1)
+            total += n
+        return int(total)
+
+    def matmul_flops_per_token(self) -> int:
+        return 2 * self.weight_elements(active_only=True)

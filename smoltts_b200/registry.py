@@ -21,6 +21,7 @@ def register_model(name: str, module: str, cls: str) -> None:
 register_model("dual_ar", "smoltts_b200.model", "RQTransformer")
 register_model("Pamasun", "smoltts_b200.lm", "PamasunLM")
 register_model("Maferax", "smoltts_b200.lm", "MaferaxLM")
+register_model("Sunutar", "smoltts_b200.lm", "SunutarLM")
 
 
 def registered() -> Dict[str, Tuple[str, str]]:
