@@ -116,7 +116,8 @@ typedef struct SmolLmLayer {
     /* --- every mixer --- */
     const float* in_bias;     /* bias of the fused input projection [rows of w_in] (NULL: none) */
     const float* out_bias;    /* added to the output projection's result [width] (NULL: none) */
-    float mix_scale;          /* multiplies the mixer's result before the output projection (0 reads as 1) */
+    float mix_scale;          /* softmax attention and state-space recurrence: multiplies the mixer's result before the
+                                 output projection (used as it is: set it to 1 for a plain mixer) */
     /* A second mixer that runs beside this one on the same input (HOST pointer, copied by create; NULL: none).  Only its
      * mixer fields are read.  w_in then holds the rows of this mixer followed by the side mixer's, in_bias likewise, and
      * w_out is [width, this mixer's columns + the side mixer's columns]: the two results, each times its mix_scale, are

@@ -1985,7 +1985,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.has_gate = M.no_gate ? 0 : 1;
             A.q_norm = M.q_norm; A.k_norm = M.k_norm; A.r1 = M.dist_r1; A.r2 = M.dist_r2; A.sink = M.sink;
             A.slope = M.dist_slope; A.window = M.window; A.softcap = M.softcap;
-            A.out_ld = mix_ld; A.out_scale = M.mix_scale != 0.0f ? M.mix_scale : 1.0f;
+            A.out_ld = mix_ld; A.out_scale = M.mix_scale;
             if (M.norm_whole) {
                 attn_prep_whole_kernel<T><<<Tn, 128, 0, st>>>(A, qbuf, pool);
             } else {
@@ -2008,7 +2008,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             P.conv_w = M.conv_w; P.conv_b = M.conv_b; P.dt_bias = M.dt_bias; P.a_log = M.a_log; P.skip = M.skip; P.out_norm = M.out_norm;
             P.seq_start = s->seq_start; P.seq_pos0 = s->seq_pos0; P.seq_slot = s->seq_slot; P.tok_seq = s->tok_seq;
             P.slot_floats = m->slot_floats; P.conv_off = Ri.conv_off; P.n_slots = m->n_slots; P.err = err;
-            P.out_ld = mix_ld; P.out_scale = M.mix_scale != 0.0f ? M.mix_scale : 1.0f;
+            P.out_ld = mix_ld; P.out_scale = M.mix_scale;
             const dim3 cgrid(Tn, (std::max(ch, M.heads) + 127) / 128);
             ssd_conv_kernel<<<cgrid, 128, 0, st>>>(P, m->slots, conv, head);
             GlaArgs A;

@@ -142,6 +142,8 @@ class HybridLM:
 
         self._keep = []
         layers = (_capi_lm.SmolLmLayer * len(cfg.layers))()
+        for c in layers:
+            c.mix_scale = 1.0
         desc = self._describe(sd, layers, mat, vec)
         ccfg = _capi_lm.SmolLmConfig(
             dtype=_capi_lm.SMOL_LM_F32 if dt == torch.float32 else _capi_lm.SMOL_LM_BF16, vocab=cfg.vocab, width=cfg.width,

@@ -1,6 +1,6 @@
 """Prefill and decode throughput of the hybrid language-model engine at layer sizes that resemble a real model's:
 the Pamasun design beside the DualAR slow transformer (the package's closest model: attention + gated MLP layers), and the
-Maferax design beside Pamasun at equal width, depth, head count and layer pattern (``--lm-design maferax``).
+Maferax and Sunutar designs beside Pamasun at equal width, depth and head count (``--lm-design maferax`` / ``sunutar``).
 
 ``python bench.py --lm`` prints one JSON line: for every size, tokens/s of a whole-prompt prefill and of single-token
 decode steps against a filled cache, each with its distance from the roofline (matrix-product + attention flops over the
@@ -132,6 +132,116 @@ def bench_maferax(name: str, prompt: int, batch: int, decode_steps: int, warmup:
     for s in seqs:
         model.close_sequence(s)
     return {"model": f"Maferax {name}", "spec": spec, "parameters_m": round(all_w / 1e6, 1), "active_parameters_m": round(act_w / 1e6, 1),
+            "prefill": {"prompt": prompt, "tokens_per_s": prompt / ms_p * 1e3, "ms": ms_p, "tflops": flops_p / ms_p / 1e9,
+                        "of_peak": flops_p / ms_p / 1e9 / tflops},
+            "decode": {"batch": batch, "context": prompt, "tokens_per_s": batch / ms_d * 1e3, "ms_per_step": ms_d,
+                       "gbs": bytes_d / ms_d / 1e6, "of_peak": bytes_d / ms_d / 1e6 / hbm},
+            "gpu_launches": int(launches)}
+
+
+SUNUTAR_SIZES = {
+    # every layer: windowed attention heads x (dim | vdim) over kv_heads beside a state-space recurrence s_heads x (state, s_vdim)
+    # in s_groups groups; feed-forward: dense clamped gated units (ff), on every second layer routed experts (top of experts, size eff)
+    "w768": dict(width=768, layers=10, heads=12, kv_heads=4, dim=64, vdim=64, window=1024, s_heads=12, s_vdim=64, state=128, s_groups=1,
+                 ff=3072, experts=16, top=2, eff=1024, vocab=2368),
+    "w768dense": dict(width=768, layers=10, heads=12, kv_heads=4, dim=64, vdim=64, window=1024, s_heads=12, s_vdim=64, state=128, s_groups=1,
+                      ff=3072, experts=0, top=0, eff=0, vocab=2368),
+    "w1536": dict(width=1536, layers=12, heads=12, kv_heads=4, dim=128, vdim=128, window=1024, s_heads=24, s_vdim=64, state=128, s_groups=2,
+                  ff=4096, experts=32, top=4, eff=1024, vocab=8192),
+}
+
+
+def sunutar_config(width, layers, heads, kv_heads, dim, vdim, window, s_heads, s_vdim, state, s_groups, ff, experts, top, eff, vocab) -> dict:
+    ls = []
+    for i in range(layers):
+        mlp = ({"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "top": top}} if experts and i % 2
+               else {"kind": "dense", "ff": ff, "limit": 7.0})
+        ls.append({"type": "parallel", "mlp": mlp,
+                   "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window}, "scale": dim ** -0.5,
+                                      "softcap": 30.0},
+                             "right": {"heads": s_heads, "vdim": s_vdim, "state": state, "groups": s_groups, "conv": 4, "norm_groups": s_groups},
+                             "left_scale": 0.5, "right_scale": 0.5}})
+    return {"architecture": "Sunutar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": ls}
+
+
+def sunutar_state_dict(cfg, seed: int = 0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for k, s in cfg.tensor_shapes().items():
+        if k.endswith(".conv"):
+            sd[k] = (torch.randn(*s, generator=g) * 0.3).bfloat16()
+        elif len(s) == 2:
+            sd[k] = (torch.randn(*s, generator=g) * (s[1] ** -0.5)).bfloat16()
+        elif k.endswith("A_log"):
+            sd[k] = torch.log(torch.rand(s, generator=g) * 0.5 + 0.01).bfloat16()
+        elif "norm" in k or k.endswith(".D"):
+            sd[k] = torch.ones(s).bfloat16()
+        else:
+            sd[k] = (torch.randn(*s, generator=g) * 0.05).bfloat16()
+    sd["embed"] = torch.randn(*sd["embed"].shape, generator=g).bfloat16()
+    return sd
+
+
+def bench_sunutar(name: str, prompt: int, batch: int, decode_steps: int, warmup: int, steps: int, peaks) -> dict:
+    """Like bench_pamasun.  Prefill flops: matrix products of the weights one token touches, attention over the keys inside the
+    window (2 dim + 2 vdim flops per visible key and head) and the recurrence (6 state vdim per head and token); decode bytes:
+    the weights one step touches (every expert only if the batch's choices can cover them all), the keys and values inside
+    the window, and the states (read and written)."""
+    from .lm import SunutarLM
+    from .lm_config import SunutarConfig
+
+    hbm, tflops, _ = peaks
+    spec = SUNUTAR_SIZES[name]
+    cfg = SunutarConfig.from_dict(sunutar_config(**spec))
+    model = SunutarLM(cfg, dtype=torch.bfloat16, max_tokens=batch * (prompt + 64 + decode_steps), max_seqs=batch, page_size=64,
+                      max_step_tokens=2048, max_want=batch)
+    model.load_state_dict(sunutar_state_dict(cfg, 0))
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg.vocab, (batch, prompt + decode_steps), generator=g).tolist()
+    n_layers = len(cfg.layers)
+    H, G, d, dv, W = spec["heads"], spec["kv_heads"], spec["dim"], spec["vdim"], spec["window"]
+    sH, sdv, N = spec["s_heads"], spec["s_vdim"], spec["state"]
+    mm_flops = cfg.matmul_flops_per_token() - 2 * cfg.vocab * cfg.width
+
+    def prefill():
+        seq = model.open_sequence()
+        for lo in range(0, prompt, model.max_step_tokens):
+            part = toks[0][lo:min(prompt, lo + model.max_step_tokens)]
+            model.forward([(seq, part, [len(part) - 1] if lo + len(part) == prompt else [])])
+        model.close_sequence(seq)
+
+    l0 = model.launch_count
+    ms_p = _timed(prefill, warmup, steps)
+    launches = model.launch_count - l0
+    visible = sum(min(i + 1, W) for i in range(prompt))
+    flops_p = prompt * mm_flops + n_layers * (H * (2 * d + 2 * dv) * visible + 6 * sH * N * sdv * prompt)
+    seqs = [model.open_sequence() for _ in range(batch)]
+    for b, s in enumerate(seqs):
+        for lo in range(0, prompt, model.max_step_tokens):
+            model.forward([(s, toks[b][lo:min(prompt, lo + model.max_step_tokens)], [])])
+
+    def decode():
+        for i in range(decode_steps):
+            model.forward([(s, [toks[b][prompt + i]], [0]) for b, s in enumerate(seqs)])
+        for s in seqs:
+            s.length = prompt
+
+    l0 = model.launch_count
+    ms_d = _timed(decode, 2, steps) / decode_steps
+    launches += model.launch_count - l0
+    ctx = min(prompt + decode_steps / 2, W)
+    all_w, act_w = cfg.weight_elements(), cfg.weight_elements(active_only=True)
+    touched = act_w
+    if spec["experts"]:
+        per_expert = (all_w - act_w) / max(spec["experts"] - spec["top"], 1)
+        touched = all_w - per_expert * max(spec["experts"] - min(batch * spec["top"], spec["experts"]), 0)
+    kv_bytes = n_layers * G * (d + dv) * 2 * ctx * batch
+    st_bytes = n_layers * 2 * sH * N * sdv * 4 * batch
+    bytes_d = 2 * touched + kv_bytes + st_bytes
+    model.check_device_errors()
+    for s in seqs:
+        model.close_sequence(s)
+    return {"model": f"Sunutar {name}", "spec": spec, "parameters_m": round(all_w / 1e6, 1), "active_parameters_m": round(act_w / 1e6, 1),
             "prefill": {"prompt": prompt, "tokens_per_s": prompt / ms_p * 1e3, "ms": ms_p, "tflops": flops_p / ms_p / 1e9,
                         "of_peak": flops_p / ms_p / 1e9 / tflops},
             "decode": {"batch": batch, "context": prompt, "tokens_per_s": batch / ms_d * 1e3, "ms_per_step": ms_d,
@@ -310,7 +420,16 @@ def run(args, root: str) -> None:
     peaks = _peaks(root)
     t0 = time.time()
     entries: List[dict] = []
-    if getattr(args, "lm_design", "pamasun") == "maferax":
+    if getattr(args, "lm_design", "pamasun") == "sunutar":
+        # Sunutar beside Pamasun (the engine's closest design: the same block, attention and a recurrence) at equal width, depth and heads
+        names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768dense", "w1536"])]
+        for n in names:
+            for batch in (1, 4):
+                entries.append(bench_sunutar(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+        for n in sorted({"w1536" if n == "w1536" else "w768" for n in names}):
+            for batch in (1, 4):
+                entries.append(bench_pamasun(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+    elif getattr(args, "lm_design", "pamasun") == "maferax":
         # Maferax beside Pamasun (the engine's closest design) at equal width, depth, heads and layer pattern
         names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768dense", "w1536"])]
         for n in names:
