@@ -1861,7 +1861,7 @@ static cudaError_t launch_scan(const DeltaArgs& A, int n_seqs, const float* dec,
 
 template <int DK>
 static cudaError_t launch_gla_scan(const GlaArgs& A, int n_seqs, const float* dec, float* pool, float* o_raw, cudaStream_t st) {
-    constexpr int CB = delta_block_cols(DK), threads = CB * delta_lanes(DK);
+    constexpr int CB = gla_block_cols(DK), threads = CB * gla_lanes(DK);
     const int groups = (A.dv + CB - 1) / CB;
     if (A.head_decay) gla_scan_kernel<DK, true><<<n_seqs * A.H * groups, threads, 2 * gla_buf_floats(DK) * sizeof(float), st>>>(A, dec, pool, o_raw);
     else gla_scan_kernel<DK, false><<<n_seqs * A.H * groups, threads, 2 * gla_buf_floats(DK) * sizeof(float), st>>>(A, dec, pool, o_raw);
@@ -1998,18 +1998,18 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             else launch_attention<T, 16>(m, s, A, flash, qbuf, pool, mix_at, st);
             return SMOL_OK;
         };
-        // State-space recurrence: convolution and per-head step / decay, the scan over the slot's state, the slot's new
-        // convolution inputs, then skip, gate and the grouped norm.
+        // State-space recurrence: convolution and per-head step / decay, the scan over the slot's state, then skip, gate and the
+        // grouped norm (whose kernel also leaves the slot's new convolution inputs).
         auto state_space = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj, const float* bias, T* mix_at) -> int {
             const int inner = M.heads * M.vdim, gn = M.bc_groups * M.n_state, ch = inner + 2 * gn;
             SsdArgs P;
             P.proj = pj; P.bias = bias; P.n_in = n_in; P.H = M.heads; P.dv = M.vdim; P.N = M.n_state; P.G = M.bc_groups;
-            P.taps = M.conv_taps; P.parts = M.norm_parts; P.n_tokens = Tn; P.eps = c.norm_eps;
+            P.taps = M.conv_taps; P.parts = M.norm_parts; P.n_tokens = Tn; P.n_seqs = s->n_seqs; P.eps = c.norm_eps;
             P.conv_w = M.conv_w; P.conv_b = M.conv_b; P.dt_bias = M.dt_bias; P.a_log = M.a_log; P.skip = M.skip; P.out_norm = M.out_norm;
             P.seq_start = s->seq_start; P.seq_pos0 = s->seq_pos0; P.seq_slot = s->seq_slot; P.tok_seq = s->tok_seq;
             P.slot_floats = m->slot_floats; P.conv_off = Ri.conv_off; P.n_slots = m->n_slots; P.err = err;
             P.out_ld = mix_ld; P.out_scale = M.mix_scale;
-            const dim3 cgrid(Tn, (std::max(ch, M.heads) + 127) / 128);
+            const dim3 cgrid(Tn, (ch + 127) / 128);
             ssd_conv_kernel<<<cgrid, 128, 0, st>>>(P, m->slots, conv, head);
             GlaArgs A;
             A.proj = pj; A.n_in = n_in; A.H = M.heads; A.d = M.n_state; A.dv = M.vdim; A.rank = 0; A.n_tokens = Tn;
@@ -2023,11 +2023,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.head_decay = head; A.head_step = head + (size_t)Tn * M.heads;
             A.out_ld = mix_ld; A.out_scale = 1.0f;
             CU(launch_gla_scan_any(A, s->n_seqs, nullptr, m->slots, oraw, st));
-            if (M.conv_taps > 1) {
-                ssd_conv_state_kernel<<<dim3(s->n_seqs, (ch + 127) / 128), 128, 0, st>>>(P, m->slots);
-                m->launches += 1;
-            }
-            ssd_out_kernel<T><<<dim3(Tn, M.norm_parts), 256, 0, st>>>(P, oraw, conv, mix_at);
+            ssd_out_kernel<T><<<dim3(Tn, M.norm_parts), 256, 0, st>>>(P, oraw, conv, mix_at, m->slots);
             m->launches += 3;
             return SMOL_OK;
         };

@@ -352,12 +352,16 @@ __global__ void gla_prep_kernel(const GlaArgs A, float* __restrict__ decay) {
 // L adjacent lanes share a column, lane q keeping the key rows 4*(e*L + q) .. +3 of it in registers (DK >= d rows; rows
 // beyond d see zero keys and queries).  q, k, w of the head and v of the block's columns come into shared memory
 // kDeltaChunk tokens at a time by cp.async, the next chunk while the current one is computed.
+// Lanes per column and columns per block of the scan: from 128 key rows on, 16 lanes share a column (8 state rows per
+// lane: a token's chain of dependent instructions is half as long as with 8 lanes, and a head spreads over twice the blocks).
+__host__ __device__ constexpr int gla_lanes(int DK) { return DK >= 128 ? 16 : DK >= 64 ? 8 : 4; }
+__host__ __device__ constexpr int gla_block_cols(int DK) { return DK * gla_lanes(DK) <= 128 ? DK : 128 / gla_lanes(DK); }
 // a buffer: q | k | w as [chunk][DK] each, v [chunk][CB], then the scalar form's decay and step [chunk] each
-__host__ __device__ constexpr int gla_buf_floats(int DK) { return kDeltaChunk * (3 * DK + delta_block_cols(DK) + 2); }
+__host__ __device__ constexpr int gla_buf_floats(int DK) { return kDeltaChunk * (3 * DK + gla_block_cols(DK) + 2); }
 
 template <int DK, int VEC, bool SCALAR>
 __device__ __forceinline__ void gla_stage(const GlaArgs& A, float* buf, int c0, int n, int h, int j0, int nc, const float* decay) {
-    constexpr int CB = delta_block_cols(DK), PL = kDeltaChunk * DK;
+    constexpr int CB = gla_block_cols(DK), PL = kDeltaChunk * DK;
     const int d = A.d, HD = A.H * d, dq = d / VEC, ncq = (nc + VEC - 1) / VEC, hs = h / A.qk_share;
     for (int idx = threadIdx.x; idx < n * dq; idx += blockDim.x) {
         const int tt = idx / dq, i = (idx - tt * dq) * VEC;
@@ -380,10 +384,10 @@ __device__ __forceinline__ void gla_stage(const GlaArgs& A, float* buf, int c0, 
 }
 
 template <int DK, bool SCALAR>
-__global__ void __launch_bounds__(delta_block_cols(DK) * delta_lanes(DK)) gla_scan_kernel(const GlaArgs A, const float* __restrict__ decay,
+__global__ void __launch_bounds__(gla_block_cols(DK) * gla_lanes(DK)) gla_scan_kernel(const GlaArgs A, const float* __restrict__ decay,
                                                                                          float* __restrict__ state_pool,
                                                                                          float* __restrict__ o_raw) {
-    constexpr int L = delta_lanes(DK), CB = delta_block_cols(DK), RV = DK / L / 4, PL = kDeltaChunk * DK;
+    constexpr int L = gla_lanes(DK), CB = gla_block_cols(DK), RV = DK / L / 4, PL = kDeltaChunk * DK;
     constexpr int kBuf = gla_buf_floats(DK);
     static_assert(DK % (4 * L) == 0, "every lane owns whole 16-byte pieces");
     extern __shared__ __align__(16) float sh[];
@@ -504,7 +508,7 @@ __global__ void gla_out_kernel(const GlaArgs A, const float* __restrict__ o_raw,
 struct SsdArgs {
     const float* proj;        // this mixer's rows of the fused projection
     const float* bias;        // of those rows, or nullptr
-    int n_in, H, dv, N, G, taps, parts, n_tokens;
+    int n_in, H, dv, N, G, taps, parts, n_tokens, n_seqs;
     float eps;
     const float *conv_w, *conv_b, *dt_bias, *a_log, *skip, *out_norm;
     const int32_t *seq_start, *seq_pos0, *seq_slot, *tok_seq;
@@ -541,8 +545,7 @@ __global__ void ssd_conv_kernel(const SsdArgs A, const float* __restrict__ slots
         }
         conv[(size_t)t * ch + c] = silu_(acc);
     }
-    if (blockIdx.y == 0 && threadIdx.x < A.H) {
-        const int h = threadIdx.x;
+    for (int h = threadIdx.x; blockIdx.y == 0 && h < A.H; h += blockDim.x) {
         const float raw = A.proj[(size_t)t * A.n_in + inner + ch + h] + (A.bias ? A.bias[inner + ch + h] : 0.0f);
         const float dt = softplus_(raw + A.dt_bias[h]);
         head[(size_t)t * A.H + h] = expf(-expf(A.a_log[h]) * dt);
@@ -550,17 +553,16 @@ __global__ void ssd_conv_kernel(const SsdArgs A, const float* __restrict__ slots
     }
 }
 
-// After the convolution of a step: the slot keeps the last taps - 1 inputs of every sequence.  Blocks (sequence, slice of
-// channels); a thread reads all it needs of the old inputs before it writes.
+// After the convolution of a step the slot keeps the last taps - 1 inputs of every sequence: channel c of sequence s.  A
+// thread reads all it needs of the old inputs before it writes.  (Runs inside ssd_out_kernel, after every reader of the
+// old inputs.)
 constexpr int kMaxTaps = 16;
-__global__ void ssd_conv_state_kernel(const SsdArgs A, float* __restrict__ slots) {
-    const int s = blockIdx.x, inner = A.H * A.dv, ch = inner + 2 * A.G * A.N, keep = A.taps - 1;
+__device__ __forceinline__ void ssd_conv_state_update(const SsdArgs& A, float* __restrict__ slots, int s, int c) {
+    const int inner = A.H * A.dv, ch = inner + 2 * A.G * A.N, keep = A.taps - 1;
     const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0, pos0 = A.seq_pos0[s];
     const int slot = A.seq_slot[s];
     if (slot < 0 || slot >= A.n_slots) return;
     float* st = slots + (size_t)slot * A.slot_floats + A.conv_off;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (c >= ch) return;
     const float bc = A.bias ? A.bias[inner + c] : 0.0f;
     float nv[kMaxTaps];
 #pragma unroll
@@ -578,9 +580,11 @@ __global__ void ssd_conv_state_kernel(const SsdArgs A, float* __restrict__ slots
 }
 
 // End of the mixer: y = o + skip_h * x, times silu(z), divided by the root mean square of its part (the H*dv channels form
-// `parts` equal parts), times out_norm, times out_scale, written in T.  Blocks (token, part).
+// `parts` equal parts), times out_norm, times out_scale, written in T.  Blocks (token, part); the first part's blocks of
+// the first n_seqs tokens then bring the slots' convolution inputs up to date, one sequence each.
 template <class T>
-__global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw, const float* __restrict__ conv, T* __restrict__ out) {
+__global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw, const float* __restrict__ conv, T* __restrict__ out,
+                               float* __restrict__ slots) {
     __shared__ float red[33];
     const int t = blockIdx.x, inner = A.H * A.dv, ch = inner + 2 * A.G * A.N, len = inner / A.parts;
     const int c0 = blockIdx.y * len;
@@ -594,6 +598,8 @@ __global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw,
     ss = block_sum(ss, red);
     const float r = A.out_scale / sqrtf(ss / (float)len + A.eps);
     for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) out[(size_t)t * A.out_ld + c] = from_f<T>(value(c) * r * A.out_norm[c]);
+    if (blockIdx.y == 0 && (int)blockIdx.x < A.n_seqs && A.taps > 1)
+        for (int c = threadIdx.x; c < ch; c += blockDim.x) ssd_conv_state_update(A, slots, blockIdx.x, c);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
