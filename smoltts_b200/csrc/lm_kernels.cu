@@ -595,7 +595,7 @@ struct AttnArgs {
     float* part;                           // [short_rows][H][n_splits][dv + 2]: running maximum, denominator, unnormalised output
     const float *bias, *slope;
     int window, has_gate, out_ld;
-    float softcap, out_scale;
+    float softcap, two_over_cap, out_scale;      // two_over_cap = 2 / softcap (0 without a cap)
 };
 
 // first key a query at `pos` sees
@@ -606,8 +606,9 @@ template <bool FAST>
 __device__ __forceinline__ float attn_score(const AttnArgs& A, float dot, int dist, float r1, float r2, float slope) {
     float s = dot * A.scale;
     if (A.softcap > 0.0f) {
-        const float z = s / A.softcap;
-        s = A.softcap * (FAST ? 1.0f - 2.0f / (__expf(2.0f * z) + 1.0f) : tanhf(z));
+        // FAST: tanh z = 1 - 2 / (e^{2z} + 1) with the hardware exponential and division (an overflowing e^{2z} gives 1)
+        if (FAST) s = A.softcap * (1.0f - __fdividef(2.0f, __expf(s * A.two_over_cap) + 1.0f));
+        else s = A.softcap * tanhf(s / A.softcap);
     }
     if (A.r1) s -= r1 * (FAST ? __logf(1.0f + r2 * (float)dist) : log1pf(r2 * (float)dist));
     if (A.slope) s -= slope * (float)dist;
@@ -1984,7 +1985,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.gate_off = (size_t)M.heads * M.dim + (size_t)M.kv_heads * (M.dim + M.vdim); A.gate_ld = M.vdim; A.gate_step = 1;
             A.has_gate = M.no_gate ? 0 : 1;
             A.q_norm = M.q_norm; A.k_norm = M.k_norm; A.r1 = M.dist_r1; A.r2 = M.dist_r2; A.sink = M.sink;
-            A.slope = M.dist_slope; A.window = M.window; A.softcap = M.softcap;
+            A.slope = M.dist_slope; A.window = M.window; A.softcap = M.softcap; A.two_over_cap = M.softcap > 0.0f ? 2.0f / M.softcap : 0.0f;
             A.out_ld = mix_ld; A.out_scale = M.mix_scale;
             if (M.norm_whole) {
                 attn_prep_whole_kernel<T><<<Tn, 128, 0, st>>>(A, qbuf, pool);
@@ -2046,7 +2047,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.page_elems = m->page_elems; A.k_off = R.k_off; A.v_off = R.v_off;
             A.H = L.heads; A.scale = L.score_scale; A.eps = c.norm_eps;
             A.n_tokens = Tn; A.err = err;
-            A.slope = nullptr; A.window = 0; A.softcap = 0.0f; A.has_gate = 1; A.out_scale = 1.0f; A.out_ld = L.heads * L.kv_rank;
+            A.slope = nullptr; A.window = 0; A.softcap = A.two_over_cap = 0.0f; A.has_gate = 1; A.out_scale = 1.0f; A.out_ld = L.heads * L.kv_rank;
             {
                 const int dk = L.kv_rank + L.rot_dim, qw = L.dim + L.rot_dim;
                 T* cq = reinterpret_cast<T*>(m->ws + m->o_cq);

@@ -353,7 +353,8 @@ __global__ void gla_prep_kernel(const GlaArgs A, float* __restrict__ decay) {
 // beyond d see zero keys and queries).  q, k, w of the head and v of the block's columns come into shared memory
 // kDeltaChunk tokens at a time by cp.async, the next chunk while the current one is computed.
 // Lanes per column and columns per block of the scan: from 128 key rows on, 16 lanes share a column (8 state rows per
-// lane: a token's chain of dependent instructions is half as long as with 8 lanes, and a head spreads over twice the blocks).
+// lane: a token's chain of dependent instructions is half as long as with 8 lanes, and a head spreads over twice the blocks;
+// 32 lanes gain another 3 % only).
 __host__ __device__ constexpr int gla_lanes(int DK) { return DK >= 128 ? 16 : DK >= 64 ? 8 : 4; }
 __host__ __device__ constexpr int gla_block_cols(int DK) { return DK * gla_lanes(DK) <= 128 ? DK : 128 / gla_lanes(DK); }
 // a buffer: q | k | w as [chunk][DK] each, v [chunk][CB], then the scalar form's decay and step [chunk] each
@@ -580,8 +581,8 @@ __device__ __forceinline__ void ssd_conv_state_update(const SsdArgs& A, float* _
 }
 
 // End of the mixer: y = o + skip_h * x, times silu(z), divided by the root mean square of its part (the H*dv channels form
-// `parts` equal parts), times out_norm, times out_scale, written in T.  Blocks (token, part); the first part's blocks of
-// the first n_seqs tokens then bring the slots' convolution inputs up to date, one sequence each.
+// `parts` equal parts), times out_norm, times out_scale, written in T.  Blocks (token, part); the blocks of the
+// first n_seqs tokens then bring the slots' convolution inputs up to date, one sequence per token index.
 template <class T>
 __global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw, const float* __restrict__ conv, T* __restrict__ out,
                                float* __restrict__ slots) {
@@ -598,8 +599,8 @@ __global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw,
     ss = block_sum(ss, red);
     const float r = A.out_scale / sqrtf(ss / (float)len + A.eps);
     for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) out[(size_t)t * A.out_ld + c] = from_f<T>(value(c) * r * A.out_norm[c]);
-    if (blockIdx.y == 0 && (int)blockIdx.x < A.n_seqs && A.taps > 1)
-        for (int c = threadIdx.x; c < ch; c += blockDim.x) ssd_conv_state_update(A, slots, blockIdx.x, c);
+    if ((int)blockIdx.x < A.n_seqs && A.taps > 1)          // the parts' blocks share a sequence's channels
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ch; c += gridDim.y * blockDim.x) ssd_conv_state_update(A, slots, blockIdx.x, c);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
