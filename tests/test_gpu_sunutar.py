@@ -391,3 +391,63 @@ def test_long_portions_take_the_large_tile_path(dtype):
     assert int((row_errs(short, want) > TOL[dtype]).sum()) <= flips
     assert int((row_errs(long, short) > (1e-4 if dtype == F32 else TOL[dtype])).sum()) <= flips
     model.check_device_errors()
+
+
+def random_config(seed):
+    """A configuration drawn at random: sizes, counts and constants all differ from layer to layer.  (A part of the
+    recurrence's norm keeps at least 8 channels: the RMS division of a single channel is a sign function, which no
+    rounding survives.)"""
+    import random
+
+    r = random.Random(seed)
+
+    def divisor(n):
+        return r.choice([d for d in range(1, n + 1) if n % d == 0])
+
+    layers = []
+    for _ in range(r.randint(2, 4)):
+        heads = r.choice([1, 2, 3, 4, 6, 8])
+        l = left(heads=heads, kv_heads=divisor(heads), dim=r.choice([8, 12, 16, 24, 32, 40, 48, 64]), vdim=r.choice([8, 12, 16, 24, 32, 40, 48, 64]),
+                 window=r.randint(2, 90), scale=r.uniform(0.1, 0.4), softcap=r.uniform(5.0, 50.0))
+        sh, sv = r.choice([1, 2, 3, 4, 6, 8]), r.choice([8, 12, 16, 24, 32, 48, 64])
+        rt = right(heads=sh, vdim=sv, state=r.choice([8, 16, 24, 32, 48, 64, 96, 128]), groups=divisor(sh), conv=r.randint(2, 4),
+                   norm_groups=r.choice([d for d in range(1, sh * sv + 1) if (sh * sv) % d == 0 and sh * sv // d >= 8]))
+        experts = r.randint(2, 12)
+        mlp = r.choice([None, dense(r.choice([24, 40, 64, 100]), r.uniform(0.5, 3.0)),
+                        moe(experts, r.randint(1, min(4, experts)), r.choice([8, 16, 24, 40]), r.uniform(0.5, 3.0))])
+        layers.append(layer(l, rt, r.uniform(0.3, 1.5), r.uniform(0.3, 1.5), mlp))
+    return config(layers, vocab=r.randint(50, 500), width=r.choice([64, 96, 128, 192, 256]), eps=r.choice([1e-6, 1e-5]), mult=r.uniform(0.2, 1.0))
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_random_configurations_in_mixed_steps(seed, dtype):
+    """Configurations drawn at random, two requests sharing steps: a prompt in portions beside single decoded tokens."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = random_config(seed)
+    model, orc, _ = engine_and_oracle(cfg, seed=20 + seed, dtype=dtype, page_size=64, max_tokens=384)
+    V = cfg["vocab"]
+    a, b_ = tokens(150, V, 50 + seed), tokens(60, V, 70 + seed)
+    want_a, want_b = orc.forward(a), orc.forward(b_)
+    tb = TokenBatcher(model)
+    got_a = [tb.feed([("a", a[:37], list(range(37)))])]
+    got_b = []
+    out = tb.feed([("a", a[37:101], list(range(64))), ("b", b_[:50], list(range(50)))])
+    got_a.append(out[:64]); got_b.append(out[64:])
+    at = 101
+    for i in range(10):                                   # "b" decodes beside portions of "a", then beside its decoding
+        n = [2, 9, 1, 17, 3, 1, 1, 1, 1, 1][i]
+        out = tb.feed([("b", b_[50 + i:51 + i], [0]), ("a", a[at:at + n], list(range(n)))])
+        got_b.append(out[:1]); got_a.append(out[1:])
+        at += n
+    got_a.append(tb.feed([("a", a[at:], list(range(150 - at)))], end=["a", "b"]))
+    model.check_device_errors()
+    for got, want in ((torch.cat(got_a), want_a), (torch.cat(got_b), want_b)):
+        errs = row_errs(got, want)
+        if dtype == F32:
+            assert float(errs.max()) < TOL[F32]
+        else:
+            # bf16: a router's close call may go the other way, and the recurrences of the layers above carry that row's
+            # difference on to later rows: the bulk of the rows is held to the tolerance, not every row
+            assert float(errs.median()) < TOL[BF16] / 4 and float((errs > TOL[BF16]).double().mean()) <= 0.15
