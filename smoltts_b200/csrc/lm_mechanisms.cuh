@@ -384,6 +384,9 @@ __device__ __forceinline__ void gla_stage(const GlaArgs& A, float* buf, int c0, 
     }
 }
 
+struct TrueType { static constexpr bool value = true; };
+struct FalseType { static constexpr bool value = false; };
+
 template <int DK, bool SCALAR>
 __global__ void __launch_bounds__(gla_block_cols(DK) * gla_lanes(DK)) gla_scan_kernel(const GlaArgs A, const float* __restrict__ decay,
                                                                                          float* __restrict__ state_pool,
@@ -438,13 +441,14 @@ __global__ void __launch_bounds__(gla_block_cols(DK) * gla_lanes(DK)) gla_scan_k
         const float* s_v = b + 3 * PL + col;
         const float* s_sc = b + 3 * PL + kDeltaChunk * CB;      // scalar form: decay [chunk], step [chunk]
         // four tokens at a time: their state updates follow one another, their sums over the key rows are then reduced side
-        // by side, so that the shuffle latency is paid once per four tokens
-        for (int tt = 0; tt < n; tt += 4) {
+        // by side, so that the shuffle latency is paid once per four tokens.  FULL: the four tokens exist (no bounds checks).
+        auto group = [&](const int tt, auto full) {
+            constexpr bool FULL = decltype(full)::value;
             float po[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 po[u] = 0.0f;
-                if (tt + u < n) {
+                if (FULL || tt + u < n) {
                     const float v = SCALAR ? s_v[(tt + u) * CB] * s_sc[kDeltaChunk + tt + u] : s_v[(tt + u) * CB];
                     const float w1 = SCALAR ? s_sc[tt + u] : 0.0f;
                     float sa = 0.0f, sb = 0.0f;
@@ -471,8 +475,15 @@ __global__ void __launch_bounds__(gla_block_cols(DK) * gla_lanes(DK)) gla_scan_k
             if (q == 0 && j < dv) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
-                    if (tt + u < n) o_raw[(size_t)(c0 + tt + u) * A.H * dv + h * dv + j] = po[u] * A.q_scale;
+                    if (FULL || tt + u < n) o_raw[(size_t)(c0 + tt + u) * A.H * dv + h * dv + j] = po[u] * A.q_scale;
             }
+        };
+        if (n == kDeltaChunk) {
+            // a whole chunk, unrolled: the next group's loads and updates are issued while this group's sums are reduced
+#pragma unroll
+            for (int tt = 0; tt < kDeltaChunk; tt += 4) group(tt, TrueType{});
+        } else {
+            for (int tt = 0; tt < n; tt += 4) group(tt, FalseType{});
         }
     }
 #pragma unroll

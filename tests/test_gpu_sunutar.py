@@ -451,3 +451,21 @@ def test_random_configurations_in_mixed_steps(seed, dtype):
             # bf16: a router's close call may go the other way, and the recurrences of the layers above carry that row's
             # difference on to later rows: the bulk of the rows is held to the tolerance, not every row
             assert float(errs.median()) < TOL[BF16] / 4 and float((errs > TOL[BF16]).double().mean()) <= 0.15
+
+
+@pytest.mark.parametrize("window", [50, 200, 450])
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_decoding_in_a_large_pool(window, dtype):
+    """A pool of 40 000 positions: the decoding attention cuts the keys into wider ranges than in a small pool, and the
+    window starts inside, at the edge of, or several ranges before the row's own."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([layer(left(heads=4, kv_heads=2, dim=16, vdim=16, window=window, scale=0.5, softcap=15.0), mlp=dense(32))], vocab=53)
+    model, orc, _ = engine_and_oracle(cfg, seed=15, dtype=dtype, edit=sharp, page_size=64, max_tokens=40000, max_step_tokens=512)
+    toks = tokens(520, 53, 6)
+    want = orc.forward(toks)
+    b = TokenBatcher(model)
+    outs = [b.feed([("x", toks[:370], list(range(370)))]), b.feed([("x", toks[370:377], list(range(7)))])]
+    outs += [b.feed([("x", [t], [0])]) for t in toks[377:]]
+    b.close()
+    assert rel_err(torch.cat(outs), want) < TOL[dtype]
