@@ -663,19 +663,35 @@ __global__ void attn_prep_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __re
 }
 
 // The same preparation with query and key norms over the WHOLE projection: one root mean square for all query heads of a
-// token (weights q_norm [H*d]) and one for all key heads (k_norm [G*d]).  One block per token.
+// token (weights q_norm [H*d]) and one for all key heads (k_norm [G*d]).  One block per token.  Loads go out kPrepBatch
+// at a time before their first use: a lone token (decoding) waits for memory a few times, not once per element.
+constexpr int kPrepBatch = 4;
+
 template <class T>
-__global__ void attn_prep_whole_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __restrict__ pool) {
+__global__ void __launch_bounds__(256) attn_prep_whole_kernel(const AttnArgs A, T* __restrict__ qbuf, T* __restrict__ pool) {
     __shared__ float red[2][33];
     const int t = blockIdx.x, nq = A.H * A.d, nk = A.G * A.d, nv = A.G * A.dv;
     const float* row = A.proj + (size_t)t * A.n_in;
     const int pos = A.tok_pos[t];
     const int pg = pos / A.page_size, in_pg = pos % A.page_size;
     const int page = pg < A.max_pages ? A.block_table[(size_t)A.tok_seq[t] * A.max_pages + pg] : -1;
-    auto at = [&](int c) { return row[c] + (A.bias ? A.bias[c] : 0.0f); };
-    float sq = 0.0f, sk = 0.0f;
-    for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = at(c); sq += v * v; }
-    for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = at(nq + c); sk += v * v; }
+    // sum of squares of row[lo .. lo + n) + bias
+    auto sum_sq = [&](int lo, int n) {
+        float ss = 0.0f;
+        for (int c0 = threadIdx.x; c0 < n; c0 += blockDim.x * kPrepBatch) {
+            float v[kPrepBatch], bv[kPrepBatch];
+#pragma unroll
+            for (int u = 0; u < kPrepBatch; ++u) {
+                const int c = c0 + u * blockDim.x;
+                v[u] = c < n ? row[lo + c] : 0.0f;
+                bv[u] = (c < n && A.bias) ? A.bias[lo + c] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < kPrepBatch; ++u) ss = fmaf(v[u] + bv[u], v[u] + bv[u], ss);
+        }
+        return ss;
+    };
+    float sq = sum_sq(0, nq), sk = sum_sq(nq, nk);
     sq = warp_sum(sq);
     sk = warp_sum(sk);
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
@@ -685,20 +701,37 @@ __global__ void attn_prep_whole_kernel(const AttnArgs A, T* __restrict__ qbuf, T
     sk = 0.0f;
     for (int i = 0; i < nw; ++i) { sq += red[0][i]; sk += red[1][i]; }      // the same order in every thread
     const float rq = 1.0f / sqrtf(sq / (float)nq + A.eps), rk = 1.0f / sqrtf(sk / (float)nk + A.eps);
-    for (int c = threadIdx.x; c < nq; c += blockDim.x) qbuf[(size_t)t * nq + c] = from_f<T>(at(c) * rq * A.q_norm[c]);
+    // element c of row[lo ..) + bias, times mul, times weight[c] (nullptr: 1) -> store(c, value)
+    auto emit = [&](int lo, int n, float mul, const float* weight, auto store) {
+        for (int c0 = threadIdx.x; c0 < n; c0 += blockDim.x * kPrepBatch) {
+            float v[kPrepBatch], wv[kPrepBatch];
+#pragma unroll
+            for (int u = 0; u < kPrepBatch; ++u) {
+                const int c = c0 + u * blockDim.x;
+                v[u] = c < n ? row[lo + c] + (A.bias ? A.bias[lo + c] : 0.0f) : 0.0f;
+                wv[u] = (c < n && weight) ? weight[c] : 1.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < kPrepBatch; ++u) {
+                const int c = c0 + u * blockDim.x;
+                if (c < n) store(c, v[u] * mul * wv[u]);
+            }
+        }
+    };
+    emit(0, nq, rq, A.q_norm, [&](int c, float v) { qbuf[(size_t)t * nq + c] = from_f<T>(v); });
     if (page < 0 || page >= A.n_pages) {
         if (threadIdx.x == 0) atomicExch(A.err, 1);
         return;
     }
     T* base = pool + (size_t)page * A.page_elems;
-    for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+    emit(nq, nk, rk, A.k_norm, [&](int c, float v) {
         const int g = c / A.d, i = c - g * A.d;
-        base[A.k_off + ((size_t)g * A.page_size + in_pg) * A.d + i] = from_f<T>(at(nq + c) * rk * A.k_norm[c]);
-    }
-    for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+        base[A.k_off + ((size_t)g * A.page_size + in_pg) * A.d + i] = from_f<T>(v);
+    });
+    emit(nq + nk, nv, 1.0f, nullptr, [&](int c, float v) {
         const int g = c / A.dv, i = c - g * A.dv;
-        base[A.v_off + ((size_t)g * A.page_size + in_pg) * A.dv + i] = from_f<T>(at(nq + nk + c));
-    }
+        base[A.v_off + ((size_t)g * A.page_size + in_pg) * A.dv + i] = from_f<T>(v);
+    });
 }
 
 // One warp per (token, query head), 32 keys per round: lane j scores key j (full dot product, the query in shared
@@ -1988,7 +2021,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.slope = M.dist_slope; A.window = M.window; A.softcap = M.softcap; A.two_over_cap = M.softcap > 0.0f ? 2.0f / M.softcap : 0.0f;
             A.out_ld = mix_ld; A.out_scale = M.mix_scale;
             if (M.norm_whole) {
-                attn_prep_whole_kernel<T><<<Tn, 128, 0, st>>>(A, qbuf, pool);
+                attn_prep_whole_kernel<T><<<Tn, Tn > 64 ? 128 : 256, 0, st>>>(A, qbuf, pool);      // few tokens: more loads in flight per token
             } else {
                 const int units = Tn * (M.heads + 2 * M.kv_heads);
                 attn_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(A, qbuf, pool);

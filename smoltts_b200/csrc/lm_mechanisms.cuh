@@ -601,15 +601,47 @@ __global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw,
     const int t = blockIdx.x, inner = A.H * A.dv, ch = inner + 2 * A.G * A.N, len = inner / A.parts;
     const int c0 = blockIdx.y * len;
     const float* z = A.proj + (size_t)t * A.n_in;
+    // a part's values in registers where it has at most 4 per thread (all loads issued before the first use), else recomputed
+    constexpr int R = 4;
+    const bool in_regs = len <= (int)blockDim.x * R;
     auto value = [&](int c) {
         const float zz = z[c] + (A.bias ? A.bias[c] : 0.0f);
         return (o_raw[(size_t)t * inner + c] + A.skip[c / A.dv] * conv[(size_t)t * ch + c]) * silu_(zz);
     };
+    float val[R], wt[R];
     float ss = 0.0f;
-    for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) { const float v = value(c); ss += v * v; }
+    if (in_regs) {
+        float zr[R], br[R], orr[R], sr[R], cr[R];
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
+            const int c = c0 + threadIdx.x + u * blockDim.x;
+            const bool in = c < c0 + len;
+            zr[u] = in ? z[c] : 0.0f;
+            br[u] = (in && A.bias) ? A.bias[c] : 0.0f;
+            orr[u] = in ? o_raw[(size_t)t * inner + c] : 0.0f;
+            sr[u] = in ? A.skip[c / A.dv] : 0.0f;
+            cr[u] = in ? conv[(size_t)t * ch + c] : 0.0f;
+            wt[u] = in ? A.out_norm[c] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
+            val[u] = (orr[u] + sr[u] * cr[u]) * silu_(zr[u] + br[u]);
+            ss = fmaf(val[u], val[u], ss);
+        }
+    } else {
+        for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) { const float v = value(c); ss += v * v; }
+    }
     ss = block_sum(ss, red);
     const float r = A.out_scale / sqrtf(ss / (float)len + A.eps);
-    for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) out[(size_t)t * A.out_ld + c] = from_f<T>(value(c) * r * A.out_norm[c]);
+    if (in_regs) {
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
+            const int c = c0 + threadIdx.x + u * blockDim.x;
+            if (c < c0 + len) out[(size_t)t * A.out_ld + c] = from_f<T>(val[u] * r * wt[u]);
+        }
+    } else {
+        for (int c = c0 + threadIdx.x; c < c0 + len; c += blockDim.x) out[(size_t)t * A.out_ld + c] = from_f<T>(value(c) * r * A.out_norm[c]);
+    }
     if ((int)blockIdx.x < A.n_seqs && A.taps > 1)          // the parts' blocks share a sequence's channels
         for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ch; c += gridDim.y * blockDim.x) ssd_conv_state_update(A, slots, blockIdx.x, c);
 }
