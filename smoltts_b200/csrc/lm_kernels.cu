@@ -93,17 +93,38 @@ __global__ void norm_rows_kernel(const float* __restrict__ x, const int32_t* __r
 
 // End of a sublayer fused with the start of the next one:
 //   x <- x + ls * (y / rms(y) * (woff + wb));   hn <- x / rms(x) * (woff + wn)     (wn == nullptr: no next norm)
-// yb != nullptr: a bias [D] joins y first (the output projection's).  One block per row; the new row is kept in shared
-// memory between the two passes.
+// yb != nullptr: a bias [D] joins y first (the output projection's).  rs.yp != nullptr: y is instead the routed experts'
+// weighted sum, taken here (hin: the sublayer's input, which identity outputs hand on).  One block per row; the new row
+// is kept in shared memory between the two passes.
 constexpr int kRowRegs = 8;   // add_norm keeps a row in registers when it has at most 8 elements per thread
+
+// The sublayer's output of a routed feed-forward, summed on the fly by the norm kernel that follows it: for the `top`
+// choices k of a token (ascending), weight[k] * (row slot_of[k] of the experts' outputs, or the token's input itself where
+// slot_of[k] < 0: an identity output).  sel_w == nullptr: every weight is 1 (the weights went into the experts' inputs).
+struct RoutedSum {
+    const float* yp;              // nullptr: the sublayer's output is y
+    const int32_t* slot_of;
+    const float* sel_w;
+    int top;
+};
 
 template <class T>
 __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
                                 const float* __restrict__ ls, const float* __restrict__ wn, float eps, int D, T* __restrict__ hn,
-                                const float woff, const float* __restrict__ yb) {
+                                const float woff, const float* __restrict__ yb, const RoutedSum rs, const T* hin) {
     extern __shared__ float row[];
     __shared__ float red[33];
     const size_t o = (size_t)blockIdx.x * D;
+    auto y_at = [&](int c) -> float {
+        if (!rs.yp) return y[o + c] + (yb ? yb[c] : 0.0f);
+        float acc = 0.0f;
+        for (int k = 0; k < rs.top; ++k) {
+            const int slot = rs.slot_of[(size_t)blockIdx.x * rs.top + k];
+            const float v = slot >= 0 ? rs.yp[(size_t)slot * D + c] : to_f<T>(hin[o + c]);
+            acc = fmaf(rs.sel_w ? rs.sel_w[(size_t)blockIdx.x * rs.top + k] : 1.0f, v, acc);
+        }
+        return acc;
+    };
     if (D <= (int)blockDim.x * kRowRegs) {
         // every operand is loaded before the first reduction: the kernel waits for global memory once
         float yv[kRowRegs], xv[kRowRegs], lv[kRowRegs], bv[kRowRegs], nv[kRowRegs];
@@ -112,7 +133,7 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
         for (int i = 0; i < kRowRegs; ++i) {
             const int c = threadIdx.x + i * blockDim.x;
             const bool in = c < D;
-            yv[i] = in ? y[o + c] + (yb ? yb[c] : 0.0f) : 0.0f;
+            yv[i] = in ? y_at(c) : 0.0f;
             xv[i] = in ? x[o + c] : 0.0f;
             lv[i] = in ? ls[c] : 0.0f;
             bv[i] = in ? wb[c] : 0.0f;
@@ -143,12 +164,13 @@ __global__ void add_norm_kernel(float* __restrict__ x, const float* __restrict__
         return;
     }
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) { const float v = y[o + c] + (yb ? yb[c] : 0.0f); ss += v * v; }
+    float* ysum = row;            // the sublayer's output of this row, then the new row
+    for (int c = threadIdx.x; c < D; c += blockDim.x) { const float v = y_at(c); ysum[c] = v; ss += v * v; }
     ss = block_sum(ss, red);
     const float r = 1.0f / sqrtf(ss / (float)D + eps);
     float s2 = 0.0f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        const float v = x[o + c] + ls[c] * ((y[o + c] + (yb ? yb[c] : 0.0f)) * r * (woff + wb[c]));
+        const float v = x[o + c] + ls[c] * (ysum[c] * r * (woff + wb[c]));
         x[o + c] = v;
         row[c] = v;
         s2 += v * v;
@@ -2251,12 +2273,8 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 } else {
                     CU(cudaMemsetAsync(slot_of, 0xff, (size_t)pairs * 4, st));
                 }
-                if (postnorm) {
-                    routed.yp = yp; routed.slot_of = slot_of; routed.sel_w = sel_w; routed.top = L.top_k;      // summed by the norm that follows
-                } else {
-                    moe_combine_kernel<T><<<Tn, nthr, 0, st>>>(hn, yp, slot_of, L.route_input ? nullptr : sel_w, L.top_k, D, y);
-                    m->launches += 1;
-                }
+                // summed by the norm that follows
+                routed.yp = yp; routed.slot_of = slot_of; routed.sel_w = L.route_input ? nullptr : sel_w; routed.top = L.top_k;
             }
             return SMOL_OK;
         };
@@ -2275,13 +2293,13 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 m->launches += 1;
             }
         } else if (L.mlp != SMOL_LM_MLP_NONE) {
-            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, L.norm2, c.norm_eps, D, hn, woff, L.out_bias);
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, L.norm2, c.norm_eps, D, hn, woff, L.out_bias, no_sum, hn);
             const int rc = feed_forward();
             if (rc != SMOL_OK) return rc;
-            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm2b, L.ls2, next_norm1, c.norm_eps, D, hn, woff, nullptr);
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm2b, L.ls2, next_norm1, c.norm_eps, D, hn, woff, nullptr, routed, hn);
             m->launches += 2;
         } else {
-            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, next_norm1, c.norm_eps, D, hn, woff, L.out_bias);
+            add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, next_norm1, c.norm_eps, D, hn, woff, L.out_bias, no_sum, hn);
             m->launches += 1;
         }
         if (s->trace) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));

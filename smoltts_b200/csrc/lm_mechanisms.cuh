@@ -68,14 +68,7 @@ __global__ void embed_gain_norm_kernel(const int32_t* __restrict__ tokens, const
 // sum_j mix[j] * history[j] over the n_hist entries (entry 0: the embedding output), summed in ascending j.
 // `rows` selects rows (final norm of the wanted rows): then only hn is written, y is not read, and alpha multiplies the
 // result instead (the scale of the logits, applied before the head's product).
-// The sublayer's output of a routed feed-forward, summed on the fly: for the `top` choices k of a token (ascending),
-// weight[k] * (row slot_of[k] of the experts' outputs, or the token's input itself where slot_of[k] < 0: an identity output).
-struct RoutedSum {
-    const float* yp;              // nullptr: the sublayer's output is y
-    const int32_t* slot_of;
-    const float* sel_w;
-    int top;
-};
+// (RoutedSum, the sublayer's output of a routed feed-forward summed on the fly, is declared beside add_norm_kernel.)
 
 template <class T>
 __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha, const float* __restrict__ gain, float eps,
@@ -897,23 +890,6 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const void* __restrict__ 
     }
     acc = warp_sum(acc);
     if (lane == 0) y[(size_t)r * N + n] = acc;
-}
-
-// y[t] = sum_k w[t][k] * (expert output of pair (t, k), or the input x[t] for an identity output), k ascending.
-// sel_w == nullptr: every weight is 1 (the weights went into the experts' inputs).
-template <class TI>
-__global__ void moe_combine_kernel(const TI* __restrict__ x, const float* __restrict__ yp, const int32_t* __restrict__ slot_of,
-                                   const float* __restrict__ sel_w, int top, int D, float* __restrict__ y) {
-    const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float acc = 0.0f;
-        for (int k = 0; k < top; ++k) {
-            const int slot = slot_of[(size_t)t * top + k];
-            const float v = slot >= 0 ? yp[(size_t)slot * D + c] : to_f<TI>(x[(size_t)t * D + c]);
-            acc = fmaf(sel_w ? sel_w[(size_t)t * top + k] : 1.0f, v, acc);
-        }
-        y[(size_t)t * D + c] = acc;
-    }
 }
 
 }  // namespace lm
