@@ -390,6 +390,9 @@ def test_long_portions_take_the_large_tile_path(dtype):
     short = torch.cat([b.feed([("s", toks[lo:lo + 100], list(range(100)))], end=["s"] if lo == 600 else []) for lo in range(0, 700, 100)])
     assert int((row_errs(short, want) > TOL[dtype]).sum()) <= flips
     assert int((row_errs(long, short) > (1e-4 if dtype == F32 else TOL[dtype])).sum()) <= flips
+    # one entry larger than the engine's step: the batcher cuts it into engine steps itself
+    once = b.feed([("w", toks, list(range(700)))], end=["w"])
+    assert int((row_errs(once, want) > TOL[dtype]).sum()) <= flips
     model.check_device_errors()
 
 
