@@ -14,13 +14,15 @@ from pathlib import Path
 from typing import Any, Dict, List, Optional
 
 # values of SMOL_LM_MIX_* (include/smoltts_b200_lm.h)
-MIXER_KINDS = {"attention": 0, "general_delta": 1, "latent_attention": 2, "gla": 3, "state_space": 4}
+MIXER_KINDS = {"attention": 0, "general_delta": 1, "latent_attention": 2, "gla": 3, "state_space": 4, "sigmoid_attention": 5,
+               "lightning": 6, "hgrn2": 7}
 MLP_KINDS = {None: 0, "dense": 1}                        # SMOL_LM_MLP_* of Pamasun: "dense" = up, PolyNorm, down
 # SMOL_LM_MLP_* of Maferax: "dense" = gated (tanh-form gelu), "moe" = routed mixture of gated (silu) experts
 MAFERAX_MLP_KINDS = {None: 0, "dense": 2, "moe": 3}
-ACT_GELU_TANH, ACT_SILU, ACT_CLAMPED = 0, 1, 2           # SMOL_LM_ACT_*
+ACT_GELU_TANH, ACT_SILU, ACT_CLAMPED, ACT_RELU_SQUARED = 0, 1, 2, 3      # SMOL_LM_ACT_*
 ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1                      # SMOL_LM_ROUTE_*
-BLOCK_SANDWICH, BLOCK_POSTNORM = 0, 1                    # SMOL_LM_BLOCK_*
+BLOCK_SANDWICH, BLOCK_POSTNORM, BLOCK_PRENORM = 0, 1, 2   # SMOL_LM_BLOCK_*
+NORM_RMS, NORM_DYT = 0, 1                                # SMOL_LM_NORM_*
 
 
 @dataclass
@@ -550,3 +552,295 @@ class SunutarConfig:
 
     def matmul_flops_per_token(self) -> int:
         return 2 * self.weight_elements(active_only=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Gunirax: pre-norm layers whose norm is a Dynamic Tanh (no mean, no variance: tanh(alpha x) * weight + shift); a span of
+# layers may run several times with shared weights, every pass after the first starting from stream + embedding output.
+# Mixers: a pair on the same input -- sigmoid attention (chunked mask, rotary with stretched frequencies, weightless
+# query/key norm, values = the key projection, the heads' weight maps mixed by a matrix, one gate per head) beside
+# lightning attention (constant decay per head) -- each projected to the width, RMS-normed there and averaged; or HGRN2
+# (the forget gate also decides what is written).  Feed-forwards: gated (silu), or routed squared-relu experts with
+# grouped choice (a group's rank: its two best choice scores) plus a shared expert.
+
+
+@dataclass
+class RotarySpec:
+    base: float
+    dims: int             # leading coordinates of a head the rotation acts on, pair (2i, 2i+1) by angle pos * f_i
+    # frequency stretching (factor 0: none): wavelengths above original/low are divided by factor, those below
+    # original/high kept, the band between blended linearly in original/wavelength
+    factor: float = 0.0
+    low: float = 1.0
+    high: float = 1.0
+    original: float = 0.0
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "RotarySpec":
+        sc = d.get("scaling") or {}
+        spec = cls(float(d["base"]), int(d["dims"]), float(sc.get("factor", 0.0)), float(sc.get("low", 1.0)), float(sc.get("high", 1.0)),
+                   float(sc.get("original", 0.0)))
+        if spec.dims % 2 or spec.dims < 0:
+            raise ValueError("rotary: dims must be even")
+        return spec
+
+    def to_dict(self) -> Dict[str, Any]:
+        d: Dict[str, Any] = {"base": self.base, "dims": self.dims}
+        if self.factor:
+            d["scaling"] = {"factor": self.factor, "low": self.low, "high": self.high, "original": self.original}
+        return d
+
+    def frequencies(self) -> List[float]:
+        out = []
+        for i in range(self.dims // 2):
+            f = self.base ** (-2.0 * i / self.dims)
+            if self.factor:
+                wl = 2.0 * math.pi / f
+                if wl > self.original / self.low:
+                    f = f / self.factor
+                elif wl >= self.original / self.high:
+                    s = (self.original / wl - self.low) / (self.high - self.low)
+                    f = (1.0 - s) * f / self.factor + s * f
+            out.append(f)
+        return out
+
+
+@dataclass
+class SigmoidAttentionSpec:
+    kind = "sigmoid_attention"
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int             # = dim: the values are the key projection
+    chunk: int            # a query at i sees the keys j <= i with floor(j / chunk) == floor(i / chunk)
+    scale: float
+    rot: RotarySpec
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "SigmoidAttentionSpec":
+        spec = cls(int(d["heads"]), int(d["kv_heads"]), int(d["dim"]), int(d["vdim"]), int(d["mask"]["size"]), float(d["scale"]),
+                   RotarySpec.from_dict(d["rot"]))
+        if spec.heads % spec.kv_heads or spec.chunk < 1 or spec.vdim != spec.dim or spec.rot.dims > spec.dim:
+            raise ValueError("sigmoid attention: heads must be a multiple of kv_heads, the chunk at least 1, vdim equal to dim, rot.dims at most dim")
+        return spec
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "mask": {"size": self.chunk},
+                "scale": self.scale, "rot": self.rot.to_dict()}
+
+
+@dataclass
+class LightningSpec:
+    kind = "lightning"
+    heads: int
+    dim: int
+    vdim: int
+    decay: List[float]    # one per head
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "LightningSpec":
+        spec = cls(int(d["heads"]), int(d["dim"]), int(d["vdim"]), [float(v) for v in d["decay"]])
+        if len(spec.decay) != spec.heads:
+            raise ValueError("lightning attention: one decay per head")
+        return spec
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim, "vdim": self.vdim, "decay": list(self.decay)}
+
+
+@dataclass
+class Hgrn2Spec:
+    kind = "hgrn2"
+    heads: int
+    dim: int
+    vdim: int
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "Hgrn2Spec":
+        return cls(int(d["heads"]), int(d["dim"]), int(d["vdim"]))
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim, "vdim": self.vdim}
+
+
+@dataclass
+class GuniraxLayer:
+    kind: str                                # "parallel" | "hgrn2"
+    left: Optional[SigmoidAttentionSpec] = None
+    right: Optional[LightningSpec] = None
+    mixer: Optional[Hgrn2Spec] = None
+    mlp_kind: Optional[str] = None           # None | "dense" | "moe"
+    ff: int = 0                              # dense: feed-forward size; moe: size of one expert
+    router: Optional[RouterSpec] = None
+    shared_ff: int = 0                       # moe: size of the shared expert (0: none)
+    group_score_top = 2                      # fixed by the design: a group's rank is the sum of its two best choice scores
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "GuniraxLayer":
+        if d["type"] == "parallel":
+            L = cls("parallel", SigmoidAttentionSpec.from_dict(d["mixer"]["left"]), LightningSpec.from_dict(d["mixer"]["right"]))
+        elif d["type"] == "hgrn2":
+            L = cls("hgrn2", mixer=Hgrn2Spec.from_dict(d["mixer"]))
+        else:
+            raise ValueError(f"unknown mixer type {d['type']!r}; have ['hgrn2', 'parallel']")
+        mlp = d.get("mlp")
+        if not mlp:
+            return L
+        if mlp["kind"] == "dense":
+            L.mlp_kind, L.ff = "dense", int(mlp["ff"])
+        elif mlp["kind"] == "moe":
+            L.mlp_kind, L.ff, L.router = "moe", int(mlp["expert"]["ff"]), RouterSpec.from_dict(mlp["router"])
+            L.shared_ff = int((mlp.get("shared") or {}).get("ff", 0))
+            if L.router.identity:
+                raise ValueError("router: this design has no identity outputs")
+        else:
+            raise ValueError(f"unknown feed-forward kind {mlp['kind']!r}")
+        return L
+
+    def to_dict(self) -> Dict[str, Any]:
+        mlp = None
+        if self.mlp_kind == "dense":
+            mlp = {"kind": "dense", "ff": self.ff}
+        elif self.mlp_kind == "moe":
+            r = self.router
+            mlp = {"kind": "moe", "expert": {"ff": self.ff},
+                   "router": {"experts": r.experts, "top": r.top, "groups": {"count": r.groups, "keep": r.keep}, "scale": r.scale}}
+            if self.shared_ff:
+                mlp["shared"] = {"ff": self.shared_ff}
+        mixer = {"left": self.left.to_dict(), "right": self.right.to_dict()} if self.kind == "parallel" else self.mixer.to_dict()
+        return {"type": self.kind, "mixer": mixer, "mlp": mlp}
+
+
+@dataclass
+class GuniraxConfig:
+    architecture: str = "Gunirax"
+    vocab: int = 0
+    width: int = 0
+    embedding_scale: float = 1.0
+    norm_eps: float = 1e-6
+    layers: List[GuniraxLayer] = field(default_factory=list)
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    extra: Dict[str, Any] = field(default_factory=dict, repr=False)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "GuniraxConfig":
+        loop = d.get("loop") or {}
+        known = {"architecture", "vocab", "width", "embedding", "norm", "layers", "loop"}
+        cfg = cls(architecture=d.get("architecture", "Gunirax"), vocab=int(d["vocab"]), width=int(d["width"]),
+                  embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)), norm_eps=float(d["norm"]["eps"]),
+                  layers=[GuniraxLayer.from_dict(x) for x in d["layers"]],
+                  loop_start=int(loop.get("start", 0)), loop_stop=int(loop.get("stop", 0)), loop_times=int(loop.get("times", 1)),
+                  extra={k: v for k, v in d.items() if k not in known})
+        cfg.layer_runs()
+        return cfg
+
+    @classmethod
+    def from_pretrained(cls, pathname: str) -> "GuniraxConfig":
+        path = Path(pathname)
+        if path.is_dir():
+            path = path / "config.json"
+        with open(path, "r", encoding="utf-8") as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = dict(self.extra)
+        d.update(architecture=self.architecture, vocab=self.vocab, width=self.width, embedding={"scale": self.embedding_scale},
+                 norm={"eps": self.norm_eps}, layers=[x.to_dict() for x in self.layers],
+                 loop={"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times})
+        return d
+
+    def save(self, path: str) -> None:
+        with open(path, "w") as f:
+            json.dump(self.to_dict(), f, indent=1, sort_keys=True)
+
+    def _looped(self) -> bool:
+        n, a, b = len(self.layers), self.loop_start, self.loop_stop
+        if self.loop_times < 1:
+            raise ValueError("loop.times must be at least 1")
+        if self.loop_times == 1 or b <= a:
+            return False
+        if not 0 <= a < b <= n:
+            raise ValueError(f"loop {a}..{b} x {self.loop_times} does not fit {n} layers")
+        return True
+
+    def layer_runs(self) -> List[int]:
+        """Layer index of every layer run, in execution order."""
+        n, a, b = len(self.layers), self.loop_start, self.loop_stop
+        if not self._looped():
+            return list(range(n))
+        return list(range(a)) + list(range(a, b)) * self.loop_times + list(range(b, n))
+
+    def run_restarts(self) -> List[int]:
+        """1 for the runs that open a pass after the first (the embedding output joins the stream before them), else 0."""
+        runs = self.layer_runs()
+        out = [0] * len(runs)
+        if self._looped():
+            a, span = self.loop_start, self.loop_stop - self.loop_start
+            for rep in range(1, self.loop_times):
+                out[a + rep * span] = 1
+        return out
+
+    def tensor_shapes(self) -> Dict[str, tuple]:
+        """Checkpoint tensor names and shapes."""
+        D, V = self.width, self.vocab
+        out: Dict[str, tuple] = {"embed": (V, D), "head": (V, D)}
+
+        def norm(name):
+            out.update({name: (D,), name + ".b": (D,), name + ".alpha": ()})
+
+        norm("final.norm")
+        for i, L in enumerate(self.layers):
+            p = f"l{i}."
+            norm(p + "norm1")
+            if L.kind == "parallel":
+                a, r, q = L.left, L.right, p + "mix.left."
+                out.update({q + "q": (a.heads * a.dim, D), q + "q.b": (a.heads * a.dim,), q + "k": (a.kv_heads * a.dim, D),
+                            q + "k.b": (a.kv_heads * a.dim,), q + "talk": (a.heads, a.heads), q + "pb": (a.heads,), q + "g": (a.heads, D),
+                            q + "o": (D, a.heads * a.vdim), p + "mix.left.out": (D,), p + "mix.right.out": (D,)})
+                q = p + "mix.right."
+                out.update({q + "q": (r.heads * r.dim, D), q + "k": (r.heads * r.dim, D), q + "v": (r.heads * r.vdim, D),
+                            q + "g": (r.heads * r.vdim, D), q + "o": (D, r.heads * r.vdim), q + "norm": (r.heads * r.vdim,)})
+            else:
+                m, q = L.mixer, p + "mix."
+                out.update({q + "q": (m.heads * m.dim, D), q + "f": (m.heads * m.dim, D), q + "f.b": (m.heads * m.dim,),
+                            q + "lower": (m.heads * m.dim,), q + "v": (m.heads * m.vdim, D), q + "o": (D, m.heads * m.vdim), q + "norm": (m.vdim,)})
+            if L.mlp_kind:
+                norm(p + "norm2")
+            if L.mlp_kind == "dense":
+                out.update({p + "mlp.gate": (L.ff, D), p + "mlp.up": (L.ff, D), p + "mlp.down": (D, L.ff)})
+            elif L.mlp_kind == "moe":
+                for e in range(L.router.experts):
+                    out.update({f"{p}mlp.e{e}.up": (L.ff, D), f"{p}mlp.e{e}.down": (D, L.ff)})
+                out.update({p + "mlp.router": (L.router.experts, D), p + "mlp.correction": (L.router.experts,)})
+                if L.shared_ff:
+                    out.update({p + "mlp.shared.up": (L.shared_ff, D), p + "mlp.shared.down": (D, L.shared_ff)})
+        return out
+
+    # ---- accounting used by the benchmark ----
+    def weight_elements(self, active_only: bool = False) -> int:
+        """Matrix elements of the model without the embedding table (looped layers once: their weights are shared);
+        ``active_only``: those one token touches (``top`` experts)."""
+        total = 0
+        for k, s in self.tensor_shapes().items():
+            if len(s) != 2 or k == "embed" or k.endswith(".talk"):
+                continue
+            n = s[0] * s[1]
+            if active_only and ".mlp.e" in k:
+                L = self.layers[int(k[1:k.index(".")])]
+                n = n * L.router.top / max(L.router.experts, 1)
+            total += n
+        return int(total)
+
+    def matmul_flops_per_token(self) -> int:
+        per_layer = [0.0] * len(self.layers)
+        for k, s in self.tensor_shapes().items():
+            if len(s) != 2 or not k.startswith("l") or k.endswith(".talk"):
+                continue
+            i = int(k[1:k.index(".")])
+            n = 2.0 * s[0] * s[1]
+            if ".mlp.e" in k:
+                n = n * self.layers[i].router.top / max(self.layers[i].router.experts, 1)
+            per_layer[i] += n
+        return int(sum(per_layer[i] for i in self.layer_runs()) + 2 * self.vocab * self.width)
