@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SMOL_LM_ABI_VERSION 3
+#define SMOL_LM_ABI_VERSION 4
 
 enum { SMOL_LM_BF16 = 0, SMOL_LM_F32 = 1 };
 /* token mixers */
@@ -33,8 +33,15 @@ enum {
     SMOL_LM_MIX_LATENT_ATTENTION = 2,  /* attention through a cached latent: queries and keys/values are low-rank, part of each
                                           head's query/key is rotated by position, one gate per head */
     SMOL_LM_MIX_GATED_LINEAR = 3,      /* linear attention with a decay per key channel, state [dim, vdim] per head */
-    SMOL_LM_MIX_STATE_SPACE = 4        /* state-space recurrence with one decay per head and step: a short causal convolution in
+    SMOL_LM_MIX_STATE_SPACE = 4,       /* state-space recurrence with one decay per head and step: a short causal convolution in
                                           front, state [n_state, vdim] per head plus the convolution's last inputs in the slot */
+    SMOL_LM_MIX_SIGMOID_ATTENTION = 5, /* grouped-query attention without a softmax: the weight of a visible key is sigmoid(score +
+                                          head bias), the heads' weight maps are mixed by a [heads, heads] matrix; rotated and
+                                          norm-divided queries and keys, the values being the key projection; one gate per head */
+    SMOL_LM_MIX_LIGHTNING = 6,         /* linear attention with one constant decay per head over silu'd q, k, v; state [dim, vdim]
+                                          per head; RMS norm over all heads together and a sigmoid gate per channel */
+    SMOL_LM_MIX_HGRN2 = 7              /* linear attention whose forget gate f (bounded below per channel) also writes: key = 1 - f;
+                                          state [dim, vdim] per head; RMS norm per head */
 };
 /* feed-forward kinds */
 enum {
@@ -47,16 +54,26 @@ enum {
 enum {
     SMOL_LM_ACT_GELU_TANH = 0,
     SMOL_LM_ACT_SILU = 1,
-    SMOL_LM_ACT_CLAMPED = 2            /* g = min(gate, limit), u = clamp(up, -limit, limit): g * sigmoid(act_alpha * g) * (u + 1) */
+    SMOL_LM_ACT_CLAMPED = 2,           /* g = min(gate, limit), u = clamp(up, -limit, limit): g * sigmoid(act_alpha * g) * (u + 1) */
+    SMOL_LM_ACT_RELU_SQUARED = 3       /* max(z, 0)^2 */
 };
 /* how a router turns its logits into scores */
 enum { SMOL_LM_ROUTE_SOFTMAX = 0, SMOL_LM_ROUTE_SIGMOID = 1 };
 /* how a layer wraps its sublayers */
 enum {
     SMOL_LM_BLOCK_SANDWICH = 0,        /* x += ls * norm_b(sublayer(norm_a(x))): norms with one-plus weight vectors, layer scales */
-    SMOL_LM_BLOCK_POSTNORM = 1         /* x = g * rms_divide(alpha * x + sublayer(x)): one gain per norm; after each layer the
+    SMOL_LM_BLOCK_POSTNORM = 1,        /* x = g * rms_divide(alpha * x + sublayer(x)): one gain per norm; after each layer the
                                           stream becomes a weighted sum of the embedding output and every layer's result */
+    SMOL_LM_BLOCK_PRENORM = 2          /* x += sublayer(norm(x)) with the norm SmolLmConfig.norm_kind names; a run flagged
+                                          SMOL_LM_RUN_ADD_EMBED starts from x + the embedding output */
 };
+/* the norm of the pre-norm block */
+enum {
+    SMOL_LM_NORM_RMS = 0,              /* x / rms(x) * weight */
+    SMOL_LM_NORM_DYT = 1               /* tanh(alpha * x) * weight + shift: no mean, no variance */
+};
+/* per-run flags (SmolLmConfig.run_flags) */
+enum { SMOL_LM_RUN_ADD_EMBED = 1 };    /* the embedding output is added to the stream before this run */
 
 /* One layer: sizes, constants and weights.  Matrices (`const void*`) have the engine's element type and are [out, in]
  * row-major; vectors (`const float*`) are always fp32. */
@@ -136,6 +153,36 @@ typedef struct SmolLmLayer {
     int32_t router_score;     /* SMOL_LM_ROUTE_* (route_bias may be NULL) */
     int32_t router_plain;     /* 1: a chosen output's weight is its score itself, not the score over the chosen scores' sum */
     int32_t route_input;      /* 1: the weight multiplies the expert's input rather than its output */
+    /* --- pre-norm block: the Dynamic-Tanh norms use norm1 / norm2 as weights, with these shifts [width] and alphas (one number each) --- */
+    const float *norm1_shift, *norm1_alpha, *norm2_shift, *norm2_alpha;
+    /* --- sigmoid attention (w_in rows: q [heads*dim] | k [kv_heads*dim] | gate [heads]; in_bias as usual; vdim = dim).
+     *     Per head: q and k + bias, rotated on their leading rot_dims coordinates (pair (2i, 2i+1) by pos * f_i, f_i = rot_base^(-2i/rot_dims)
+     *     stretched as below), then divided by their root mean square; the cached value is k + bias before both.
+     *     weight_g(i, j) = sigmoid(q_i.k_j * score_scale + head_bias[g]) for j <= i with floor(j / chunk) == floor(i / chunk) (chunk 0:
+     *     every j <= i); head h applies sum_g talk[h][g] * weight_g to the values of its key/value head; times sigmoid(gate_h). --- */
+    int32_t chunk;
+    const float* head_bias;   /* [heads] */
+    const float* talk;        /* [heads][heads] fp32 */
+    /* frequency stretching (rot_stretch 0: none): wavelengths 2 pi / f above rot_original / rot_low use f / rot_stretch, those below
+     * rot_original / rot_high keep f, between them s = (rot_original / wavelength - rot_low) / (rot_high - rot_low) blends
+     * (1 - s) f / rot_stretch + s f */
+    float rot_stretch, rot_low, rot_high, rot_original;
+    /* --- lightning attention (w_in rows: q | k [heads*dim each] | v | gate [heads*vdim each]); out_norm [heads*vdim] --- */
+    const float* head_decay;  /* [heads] */
+    /* --- HGRN2 (w_in rows: q | forget [heads*dim each] | v [heads*vdim]); rate_bias [heads*dim] joins the forget rows,
+     *     f = lower + (1 - lower) sigmoid(.); out_norm [vdim] shared by the heads --- */
+    const float* forget_lower;   /* [heads*dim] */
+    /* --- mixers side by side, each with its own output projection: when proj_norm is set on the layer's own mixer, it and the
+     *     side mixer each multiply their own w_out [width, own columns]; each result is divided by its root mean square over the
+     *     width and multiplied by its proj_norm [width] and its mix_scale; the two are added.  (Pre-norm block.) --- */
+    const float* proj_norm;
+    /* --- feed-forward options --- */
+    int32_t ff_plain;         /* 1: the experts and the shared expert are down(act(up)) with no gate rows: w_experts_in is
+                                 [n_experts][ff][width], w_shared_in [shared_ff][width] */
+    int32_t group_rank_top;   /* routed: a group is ranked by the sum of its group_rank_top best choice scores (0 or 1: its best) */
+    int32_t shared_ff;        /* routed: size of an expert every token uses, added with weight 1 (0: none) */
+    const void* w_shared_in;  /* [2 * shared_ff (gate rows, up rows) or shared_ff (ff_plain)][width] */
+    const void* w_shared_out; /* [width][shared_ff] */
 } SmolLmLayer;
 
 typedef struct SmolLmConfig {
@@ -154,6 +201,8 @@ typedef struct SmolLmConfig {
     float residual_alpha;     /* post-norm block: multiplies the stream before the sublayer's output is added */
     float logit_scale;        /* multiplies the logits */
     int32_t norm_plain;       /* sandwich block: 1 = the norms' weight vectors are used as they are, 0 = one is added to them */
+    int32_t norm_kind;        /* pre-norm block: SMOL_LM_NORM_* */
+    const int32_t* run_flags; /* HOST array [n_runs] of SMOL_LM_RUN_* bits, copied by create (NULL: none set) */
 } SmolLmConfig;
 
 typedef struct SmolLmGlobals {
@@ -161,6 +210,7 @@ typedef struct SmolLmGlobals {
     const void* head;         /* [vocab, width] */
     const float* final_norm;  /* sandwich block: [width] one-plus weight; post-norm block: one gain */
     const float* embed_norm;  /* post-norm block: one gain of the norm after the embedding */
+    const float *final_norm_shift, *final_norm_alpha;   /* Dynamic-Tanh final norm: shift [width], alpha (one number) */
 } SmolLmGlobals;
 
 /* A ragged batch.  All arrays live on the device. */
@@ -184,6 +234,7 @@ typedef struct SmolLmStep {
 typedef struct SmolLm SmolLm;
 
 int smol_lm_abi_version(void);
+size_t smol_lm_struct_bytes(int which);          /* sizeof of SmolLmLayer (0), SmolLmConfig (1), SmolLmGlobals (2), SmolLmStep (3): a binding checks its mirror */
 const char* smol_lm_last_error(void);
 
 /* layers / run_layer are HOST arrays, copied.  run_layer[n] = index of the layer that run n executes. */

@@ -11,7 +11,7 @@ import os
 from . import build as _build
 from ._errors import SMOL_OK, SmolError
 
-SMOL_LM_ABI_VERSION = 3
+SMOL_LM_ABI_VERSION = 4
 SMOL_LM_BF16, SMOL_LM_F32 = 0, 1
 
 
@@ -34,18 +34,22 @@ SmolLmLayer._fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "
     (n, C.c_int32) for n in ("n_state", "bc_groups", "conv_taps", "norm_parts")] + [
     (n, C.c_void_p) for n in ("conv_w", "conv_b", "dt_bias", "a_log", "skip")] + [
     (n, C.c_float) for n in ("act_limit", "act_alpha")] + [
-    (n, C.c_int32) for n in ("router_score", "router_plain", "route_input")]
+    (n, C.c_int32) for n in ("router_score", "router_plain", "route_input")] + [
+    (n, C.c_void_p) for n in ("norm1_shift", "norm1_alpha", "norm2_shift", "norm2_alpha")] + [("chunk", C.c_int32)] + [
+    (n, C.c_void_p) for n in ("head_bias", "talk")] + [(n, C.c_float) for n in ("rot_stretch", "rot_low", "rot_high", "rot_original")] + [
+    (n, C.c_void_p) for n in ("head_decay", "forget_lower", "proj_norm")] + [
+    (n, C.c_int32) for n in ("ff_plain", "group_rank_top", "shared_ff")] + [(n, C.c_void_p) for n in ("w_shared_in", "w_shared_out")]
 
 
 class SmolLmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("dtype", "vocab", "width", "n_layers", "n_runs", "page_size", "max_step_tokens",
                                          "max_step_seqs", "max_want", "max_context", "use_graph")] + [
         ("embed_scale", C.c_float), ("norm_eps", C.c_float), ("block", C.c_int32), ("residual_alpha", C.c_float), ("logit_scale", C.c_float),
-        ("norm_plain", C.c_int32)]
+        ("norm_plain", C.c_int32), ("norm_kind", C.c_int32), ("run_flags", C.POINTER(C.c_int32))]
 
 
 class SmolLmGlobals(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("embed", "head", "final_norm", "embed_norm")]
+    _fields_ = [(n, C.c_void_p) for n in ("embed", "head", "final_norm", "embed_norm", "final_norm_shift", "final_norm_alpha")]
 
 
 class SmolLmStep(C.Structure):
@@ -56,6 +60,7 @@ class SmolLmStep(C.Structure):
 
 PROTOTYPES = {
     "smol_lm_abi_version": (C.c_int, []),
+    "smol_lm_struct_bytes": (C.c_size_t, [C.c_int]),
     "smol_lm_last_error": (C.c_char_p, []),
     "smol_lm_create": (C.c_int, [C.POINTER(SmolLmConfig), C.POINTER(SmolLmLayer), C.POINTER(C.c_int32), C.POINTER(C.c_void_p)]),
     "smol_lm_destroy": (None, [C.c_void_p]),
@@ -91,6 +96,9 @@ def load() -> C.CDLL:
         fn.argtypes = args
     if lib.smol_lm_abi_version() != SMOL_LM_ABI_VERSION:
         raise RuntimeError(f"{path}: ABI version {lib.smol_lm_abi_version()} != {SMOL_LM_ABI_VERSION}")
+    for which, mirror in enumerate((SmolLmLayer, SmolLmConfig, SmolLmGlobals, SmolLmStep)):
+        if lib.smol_lm_struct_bytes(which) != C.sizeof(mirror):
+            raise RuntimeError(f"{path}: {mirror.__name__} is {lib.smol_lm_struct_bytes(which)} bytes in the library, {C.sizeof(mirror)} in the binding")
     _lib = lib
     return lib
 

@@ -27,7 +27,7 @@ LM_LIB_PATH = os.path.join(LIB_DIR, "libsmoltts_b200_lm.so")
 TARGETS = {
     "core": (LIB_PATH, STAMP, SOURCES, HEADERS),
     "lm": (LM_LIB_PATH, os.path.join(LIB_DIR, "build_lm.stamp"), ["lm_kernels.cu"],
-           ["common.cuh", "dev_model.h", "sampler.cuh", "umma.cuh", "tmap_host.h", "lm_mechanisms.cuh",
+           ["common.cuh", "dev_model.h", "sampler.cuh", "umma.cuh", "tmap_host.h", "lm_mechanisms.cuh", "lm_sigmoid_linear.cuh",
             os.path.join("..", "..", "include", "smoltts_b200.h"), os.path.join("..", "..", "include", "smoltts_b200_lm.h")]),
 }
 

@@ -1475,6 +1475,7 @@ __global__ void __launch_bounds__(kThreads) lm_sample_kernel(const float* __rest
 }  // namespace smol
 
 #include "lm_mechanisms.cuh"
+#include "lm_sigmoid_linear.cuh"
 
 // =====================================================================================================================
 // Host side
@@ -1498,6 +1499,7 @@ struct RunInfo {
     size_t state_off = 0;          // recurrent: float offset inside a slot
     size_t freq_off = 0;           // latent attention: float offset of the run's rotation frequencies in the table
     size_t conv_off = 0;           // state-space: float offset of the convolution's last inputs inside a slot
+    int flags = 0;                 // SMOL_LM_RUN_*
 };
 
 struct SmolLm {
@@ -1511,11 +1513,13 @@ struct SmolLm {
     SmolLmGlobals g{};
     size_t page_elems = 0, slot_floats = 0, esize = 2;
     int max_in = 0, max_mix = 0, max_ff = 0, max_hd = 0, max_q = 0;
+    bool any_restart = false, any_own_proj = false;
     // workspace carving (byte offsets)
     size_t o_x, o_hn, o_proj, o_mix, o_y, o_z, o_act, o_dec, o_u, o_au, o_oraw, o_q, o_hw, o_err, o_part, total;
     // post-norm block: every layer result of the step; latent attention: query latent (T), full query (fp32 and T), query in
     // latent space (fp32), rotation frequencies; routed feed-forward: choices, sorted order, tile table, per-pair buffers
     size_t o_hist = 0, o_cq = 0, o_qf = 0, o_freq = 0;
+    size_t o_x0 = 0, o_mix2 = 0, o_y2 = 0;    // pre-norm block: the embedding output; mixers with their own output projections: the second result
     size_t o_rlogits = 0, o_rdone = 0, o_ap = 0, o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
     int max_routed = 0, max_cq = 0, max_qf = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
     std::vector<float> freq_table;
@@ -1545,14 +1549,40 @@ static int n_in_of(const SmolLmLayer& L) {
     if (L.mixer == SMOL_LM_MIX_STATE_SPACE) return 2 * L.heads * L.vdim + 2 * L.bc_groups * L.n_state + L.heads;
     if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) return L.q_rank + L.kv_rank + L.rot_dim + L.heads;
     if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) return 2 * L.heads * L.dim + 2 * L.heads * L.vdim + L.rank;
+    if (L.mixer == SMOL_LM_MIX_SIGMOID_ATTENTION) return L.heads * L.dim + L.kv_heads * L.dim + L.heads;
+    if (L.mixer == SMOL_LM_MIX_LIGHTNING) return 2 * L.heads * L.dim + 2 * L.heads * L.vdim;
+    if (L.mixer == SMOL_LM_MIX_HGRN2) return 2 * L.heads * L.dim + L.heads * L.vdim;
     return 5 * L.heads * L.dim + L.rank;
 }
 
 // columns a mixer hands to the output projection
 static int mix_cols_of(const SmolLmLayer& L) { return L.mixer == SMOL_LM_MIX_GENERAL_DELTA ? L.heads * L.dim : L.heads * L.vdim; }
-static bool pairable(const SmolLmLayer& L) { return L.mixer == SMOL_LM_MIX_SINK_ATTENTION || L.mixer == SMOL_LM_MIX_STATE_SPACE; }
+static bool pairable(const SmolLmLayer& L) {
+    return L.mixer == SMOL_LM_MIX_SINK_ATTENTION || L.mixer == SMOL_LM_MIX_STATE_SPACE || L.mixer == SMOL_LM_MIX_SIGMOID_ATTENTION ||
+           L.mixer == SMOL_LM_MIX_LIGHTNING;
+}
+// base^(-2i/dims) for the dims/2 rotated pairs, stretched band by band when L.rot_stretch is set (see the header)
+static void push_frequencies(std::vector<float>& table, const SmolLmLayer& L, bool stretch) {
+    const double two_pi = 6.283185307179586476925286766559;
+    for (int i = 0; i < L.rot_dims / 2; ++i) {
+        double f = pow((double)L.rot_base, -2.0 * i / (double)L.rot_dims);
+        if (stretch && L.rot_stretch != 0.0f) {
+            const double wl = two_pi / f, orig = L.rot_original;
+            if (wl > orig / L.rot_low) {
+                f = f / L.rot_stretch;
+            } else if (wl >= orig / L.rot_high) {
+                const double b = (orig / wl - L.rot_low) / ((double)L.rot_high - L.rot_low);
+                f = (1.0 - b) * f / L.rot_stretch + b * f;
+            }
+        }
+        table.push_back((float)f);
+    }
+}
 
 extern "C" int smol_lm_abi_version(void) { return SMOL_LM_ABI_VERSION; }
+extern "C" size_t smol_lm_struct_bytes(int which) {
+    return which == 0 ? sizeof(SmolLmLayer) : which == 1 ? sizeof(SmolLmConfig) : which == 2 ? sizeof(SmolLmGlobals) : which == 3 ? sizeof(SmolLmStep) : 0;
+}
 extern "C" const char* smol_lm_last_error(void) { return g_err.c_str(); }
 
 extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers, const int32_t* run_layer, SmolLm** out) {
@@ -1563,6 +1593,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
         return fail(SMOL_ERR_INVALID, "smol_lm_create: sizes must be positive");
     SmolLm* m = new SmolLm();
     m->cfg = *cfg;
+    m->cfg.run_flags = nullptr;      // the caller's array is read below and not kept
     m->esize = cfg->dtype == SMOL_LM_F32 ? 4 : 2;
     m->layers.assign(layers, layers + cfg->n_layers);
     m->sides.resize(cfg->n_layers);
@@ -1617,7 +1648,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             r.k_off = r.v_off = m->page_elems;
             m->page_elems += (size_t)cfg->page_size * (L.kv_rank + L.rot_dim);
             r.freq_off = m->freq_table.size();
-            for (int i = 0; i < L.rot_dims / 2; ++i) m->freq_table.push_back((float)pow((double)L.rot_base, -2.0 * i / (double)L.rot_dims));
+            push_frequencies(m->freq_table, L, false);
             m->max_q = std::max(m->max_q, L.heads * (L.kv_rank + L.rot_dim));
             m->max_heads = std::max(m->max_heads, L.heads);
             m->max_vdim = std::max(m->max_vdim, L.kv_rank);
@@ -1625,6 +1656,34 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_hd = std::max(m->max_hd, L.heads * L.vdim);
             m->max_cq = std::max(m->max_cq, L.q_rank);
             m->max_qf = std::max(m->max_qf, L.heads * (L.dim + L.rot_dim));
+        } else if (L.mixer == SMOL_LM_MIX_SIGMOID_ATTENTION) {
+            if (L.kv_heads < 1 || L.heads % L.kv_heads != 0 || L.vdim != L.dim) return fail(SMOL_ERR_INVALID, "sigmoid attention: heads must be a multiple of kv_heads and vdim equal to dim");
+            if (L.heads > kSigmoidMaxHeads || L.vdim > 32 * kAttnMaxV) return fail(SMOL_ERR_UNSUPPORTED, "sigmoid attention: more than 32 heads or a head size above 512");
+            if (L.chunk < 0 || L.rot_dims < 0 || L.rot_dims > L.dim || L.rot_dims % 2 || !L.head_bias || !L.talk)
+                return fail(SMOL_ERR_INVALID, "sigmoid attention: chunk must not be negative, rot_dims even and at most dim, head_bias and talk set");
+            r.k_off = m->page_elems;
+            r.v_off = r.k_off + (size_t)L.kv_heads * cfg->page_size * L.dim;
+            m->page_elems = r.v_off + (size_t)L.kv_heads * cfg->page_size * L.vdim;
+            r.freq_off = m->freq_table.size();
+            push_frequencies(m->freq_table, L, true);
+            m->max_q = std::max(m->max_q, L.heads * L.dim);
+            m->max_heads = std::max(m->max_heads, L.heads);
+            m->max_vdim = std::max(m->max_vdim, L.vdim);
+            m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
+        } else if (L.mixer == SMOL_LM_MIX_LIGHTNING || L.mixer == SMOL_LM_MIX_HGRN2) {
+            if (L.dim > 256) return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256");
+            if (L.vdim < 1 || !L.out_norm) return fail(SMOL_ERR_INVALID, "linear attention: vdim must be positive and out_norm set");
+            if (L.mixer == SMOL_LM_MIX_LIGHTNING && !L.head_decay) return fail(SMOL_ERR_INVALID, "lightning attention: head_decay");
+            if (L.mixer == SMOL_LM_MIX_HGRN2 && (!L.forget_lower || !L.rate_bias)) return fail(SMOL_ERR_INVALID, "HGRN2: forget_lower and rate_bias");
+            r.state_off = m->slot_floats;
+            m->slot_floats += (size_t)L.heads * L.dim * L.vdim;
+            m->slot_floats = (m->slot_floats + 3) / 4 * 4;
+            m->max_hd = std::max(m->max_hd, L.heads * std::max(L.dim, L.vdim));
+            m->max_mix = std::max(m->max_mix, L.heads * L.vdim);
+            if (L.mixer == SMOL_LM_MIX_LIGHTNING) {
+                m->max_conv = std::max(m->max_conv, 2 * L.heads * L.dim + L.heads * L.vdim);
+                m->max_ssd_heads = std::max(m->max_ssd_heads, L.heads);
+            }
         } else if (L.mixer == SMOL_LM_MIX_GATED_LINEAR) {
             if (L.dim > 256) return fail(SMOL_ERR_UNSUPPORTED, "recurrent mixer: key size above 256");
             if (L.rank < 1 || L.vdim < 1 || !(L.decay_tau > 0.0f)) return fail(SMOL_ERR_INVALID, "gated linear: rank, vdim, tau must be positive");
@@ -1643,20 +1702,37 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
         const SmolLmLayer& L = m->layers[li];
         RunInfo r, rs;
         r.layer = rs.layer = li;
+        r.flags = cfg->run_flags ? cfg->run_flags[n] : 0;
+        if (r.flags & SMOL_LM_RUN_ADD_EMBED) m->any_restart = true;
         int rc = place(L, r);
+        const bool prenorm = cfg->block == SMOL_LM_BLOCK_PRENORM;
         if (rc == SMOL_OK && L.side) {
-            if (!pairable(L) || !pairable(*L.side)) rc = fail(SMOL_ERR_UNSUPPORTED, "mixers side by side: softmax attention and the state-space recurrence only");
-            else if (cfg->block == SMOL_LM_BLOCK_POSTNORM) rc = fail(SMOL_ERR_UNSUPPORTED, "mixers side by side need the sandwich block");
+            if (!pairable(L) || !pairable(*L.side)) rc = fail(SMOL_ERR_UNSUPPORTED, "mixers side by side: softmax or sigmoid attention, the state-space recurrence, lightning attention");
+            else if (cfg->block == SMOL_LM_BLOCK_POSTNORM) rc = fail(SMOL_ERR_UNSUPPORTED, "mixers side by side need the sandwich or the pre-norm block");
+            else if (L.proj_norm && (!prenorm || !L.side->proj_norm || !L.side->w_out)) rc = fail(SMOL_ERR_INVALID, "proj_norm: the pre-norm block, and set on both mixers with their own w_out");
             else rc = place(*L.side, rs);
             if (rc == SMOL_OK) m->max_mix = std::max(m->max_mix, mix_cols_of(L) + mix_cols_of(*L.side));
+            if (rc == SMOL_OK && L.proj_norm) m->any_own_proj = true;
         }
+        if (rc == SMOL_OK && prenorm) {
+            if (cfg->norm_kind != SMOL_LM_NORM_RMS && cfg->norm_kind != SMOL_LM_NORM_DYT) rc = fail(SMOL_ERR_INVALID, "pre-norm block: unknown norm kind");
+            else if (!L.norm1 || (L.mlp != SMOL_LM_MLP_NONE && !L.norm2)) rc = fail(SMOL_ERR_INVALID, "pre-norm block: norm weights");
+            else if (cfg->norm_kind == SMOL_LM_NORM_DYT && (!L.norm1_shift || !L.norm1_alpha || (L.mlp != SMOL_LM_MLP_NONE && (!L.norm2_shift || !L.norm2_alpha))))
+                rc = fail(SMOL_ERR_INVALID, "pre-norm block: the Dynamic-Tanh norms need shifts and alphas");
+            else if (L.mlp == SMOL_LM_MLP_POLYNORM || L.route_input || L.out_bias || L.n_identity > 0)
+                rc = fail(SMOL_ERR_UNSUPPORTED, "pre-norm block: PolyNorm feed-forwards, input-weighted routing, identity outputs and out_bias are not built");
+        }
+        if (rc == SMOL_OK && !prenorm && (L.shared_ff > 0 || L.proj_norm || (r.flags & SMOL_LM_RUN_ADD_EMBED) || L.mixer >= SMOL_LM_MIX_SIGMOID_ATTENTION ||
+                                         (L.side && L.side->mixer >= SMOL_LM_MIX_SIGMOID_ATTENTION)))
+            rc = fail(SMOL_ERR_UNSUPPORTED, "shared experts, proj_norm, restarting runs, sigmoid / lightning attention and HGRN2 need the pre-norm block");
+        if (rc == SMOL_OK && L.shared_ff > 0 && (L.mlp != SMOL_LM_MLP_EXPERTS || !L.w_shared_in || !L.w_shared_out)) rc = fail(SMOL_ERR_INVALID, "shared expert: routed feed-forwards only, with both matrices");
         if (rc == SMOL_OK && cfg->block == SMOL_LM_BLOCK_POSTNORM && (L.out_bias || L.route_input))
             rc = fail(SMOL_ERR_UNSUPPORTED, "out_bias and route_input need the sandwich block");
         if (rc != SMOL_OK) { delete m; return rc; }
         if (L.mlp < SMOL_LM_MLP_NONE || L.mlp > SMOL_LM_MLP_EXPERTS) { delete m; return fail(SMOL_ERR_UNSUPPORTED, "unknown feed-forward kind"); }
         if (L.mlp == SMOL_LM_MLP_POLYNORM) m->max_ff = std::max(m->max_ff, L.ff);
         if (L.mlp == SMOL_LM_MLP_GATED || L.mlp == SMOL_LM_MLP_EXPERTS) {
-            if (L.ff < 1 || L.mlp_act < SMOL_LM_ACT_GELU_TANH || L.mlp_act > SMOL_LM_ACT_CLAMPED) { delete m; return fail(SMOL_ERR_INVALID, "gated feed-forward: ff and activation"); }
+            if (L.ff < 1 || L.mlp_act < SMOL_LM_ACT_GELU_TANH || L.mlp_act > SMOL_LM_ACT_RELU_SQUARED) { delete m; return fail(SMOL_ERR_INVALID, "gated feed-forward: ff and activation"); }
         }
         if (L.mlp == SMOL_LM_MLP_GATED) m->max_ff = std::max(m->max_ff, 2 * L.ff);
         if (L.mlp == SMOL_LM_MLP_EXPERTS) {
@@ -1670,6 +1746,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->max_routed = std::max(m->max_routed, E);
             m->max_experts = std::max(m->max_experts, L.n_experts);
             m->max_pair_ff = std::max(m->max_pair_ff, L.top_k * L.ff);
+            if (L.shared_ff > 0) m->max_ff = std::max(m->max_ff, (L.ff_plain ? 1 : 2) * L.shared_ff);
         }
         m->max_in = std::max(m->max_in, n_in_of(L) + (L.side ? n_in_of(*L.side) : 0));
         m->runs.push_back(r);
@@ -1704,7 +1781,12 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     if (m->max_cq > 0) {
         m->o_cq = carve(T * (size_t)m->max_cq * E);
         m->o_qf = carve(T * (size_t)m->max_qf * 4);
-        m->o_freq = carve(m->freq_table.size() * 4 + 4);
+    }
+    if (!m->freq_table.empty()) m->o_freq = carve(m->freq_table.size() * 4 + 4);
+    if (m->any_restart) m->o_x0 = carve(T * D * 4);
+    if (m->any_own_proj) {
+        m->o_mix2 = carve(T * (size_t)std::max(m->max_mix, 1) * E);
+        m->o_y2 = carve(T * D * 4);
     }
     if (m->max_conv > 0) {
         m->o_conv = carve(T * (size_t)m->max_conv * 4);
@@ -1757,6 +1839,8 @@ static cudaError_t set_kernel_attributes() {
     if (e == cudaSuccess) e = scan_attribute<256>();
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_attn_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_attn_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<128, 128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(128, 128, false));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<192, 128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(192, 128, true));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<192, 192, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(192, 192, true));
@@ -1794,6 +1878,12 @@ extern "C" int smol_lm_bind(SmolLm* m, const SmolLmGlobals* g, void* d_workspace
     if (!m->freq_table.empty())
         CU(cudaMemcpy(m->ws + m->o_freq, m->freq_table.data(), m->freq_table.size() * sizeof(float), cudaMemcpyHostToDevice));
     if (m->cfg.block == SMOL_LM_BLOCK_POSTNORM && !g->embed_norm) return fail(SMOL_ERR_INVALID, "smol_lm_bind: the post-norm block needs embed_norm");
+    if (m->cfg.block == SMOL_LM_BLOCK_PRENORM && m->cfg.norm_kind == SMOL_LM_NORM_DYT && (!g->final_norm_shift || !g->final_norm_alpha))
+        return fail(SMOL_ERR_INVALID, "smol_lm_bind: the Dynamic-Tanh final norm needs its shift and alpha");
+    if ((size_t)m->cfg.width * 4 > 48 * 1024) {
+        CU(cudaFuncSetAttribute(residual_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->cfg.width * 4));
+        CU(cudaFuncSetAttribute(residual_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, m->cfg.width * 4));
+    }
     m->bound = true;
     return SMOL_OK;
 }
@@ -2003,7 +2093,12 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
     float* hist = reinterpret_cast<float*>(m->ws + m->o_hist);
     T* pool = static_cast<T*>(m->pages);
     const int nthr = D >= 1024 ? 256 : 128;
-    const bool postnorm = c.block == SMOL_LM_BLOCK_POSTNORM;
+    const bool postnorm = c.block == SMOL_LM_BLOCK_POSTNORM, prenorm = c.block == SMOL_LM_BLOCK_PRENORM;
+    float* x0 = m->any_restart ? reinterpret_cast<float*>(m->ws + m->o_x0) : nullptr;
+    T* mix2 = reinterpret_cast<T*>(m->ws + m->o_mix2);
+    float* y2 = reinterpret_cast<float*>(m->ws + m->o_y2);
+    auto norm_of = [&](const float* w, const float* shift, const float* alpha) { return NormSpec{c.norm_kind, w, shift, alpha, c.norm_eps}; };
+    const NormSpec no_norm{c.norm_kind, nullptr, nullptr, nullptr, c.norm_eps};
     const size_t hist_stride = (size_t)Tn * D;
     constexpr bool kIsF32 = sizeof(T) == 4;
     const float woff = c.norm_plain ? 0.0f : 1.0f;
@@ -2013,6 +2108,10 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
 
     if (postnorm) {
         embed_gain_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), D, c.vocab, m->g.embed_norm, c.norm_eps, x, hist, hn);
+    } else if (prenorm) {
+        const SmolLmLayer& L0 = m->layers[m->runs[0].layer];
+        embed_prenorm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), c.embed_scale, D, c.vocab,
+                                                     norm_of(L0.norm1, L0.norm1_shift, L0.norm1_alpha), x, x0, hn);
     } else {
         embed_norm_kernel<T><<<Tn, nthr, 0, st>>>(s->tokens, static_cast<const T*>(m->g.embed), c.embed_scale, D, c.vocab,
                                                   m->layers[m->runs[0].layer].norm1, c.norm_eps, x, hn, woff);
@@ -2025,6 +2124,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
         CU(linear<T>(m, hn, static_cast<const T*>(L.w_in), proj, Tn, n_in, D, st));
         const int mix_ld = mix_cols_of(L) + (L.side ? mix_cols_of(*L.side) : 0);      // row stride of the mixers' shared result
         int mix_cols;
+        int out_ld_now = mix_ld;        // row stride of the buffer the current mixer writes
         const T* mix_in = mix;          // what the output projection reads
         // Softmax attention over keys and values in the paged pool.  pj / bias: this mixer's rows of the fused projection.
         auto attention = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj, const float* bias, T* mix_at) -> int {
@@ -2041,7 +2141,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.has_gate = M.no_gate ? 0 : 1;
             A.q_norm = M.q_norm; A.k_norm = M.k_norm; A.r1 = M.dist_r1; A.r2 = M.dist_r2; A.sink = M.sink;
             A.slope = M.dist_slope; A.window = M.window; A.softcap = M.softcap; A.two_over_cap = M.softcap > 0.0f ? 2.0f / M.softcap : 0.0f;
-            A.out_ld = mix_ld; A.out_scale = M.mix_scale;
+            A.out_ld = out_ld_now; A.out_scale = M.mix_scale;
             if (M.norm_whole) {
                 attn_prep_whole_kernel<T><<<Tn, Tn > 64 ? 128 : 256, 0, st>>>(A, qbuf, pool);      // few tokens: more loads in flight per token
             } else {
@@ -2064,7 +2164,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             P.conv_w = M.conv_w; P.conv_b = M.conv_b; P.dt_bias = M.dt_bias; P.a_log = M.a_log; P.skip = M.skip; P.out_norm = M.out_norm;
             P.seq_start = s->seq_start; P.seq_pos0 = s->seq_pos0; P.seq_slot = s->seq_slot; P.tok_seq = s->tok_seq;
             P.slot_floats = m->slot_floats; P.conv_off = Ri.conv_off; P.n_slots = m->n_slots; P.err = err;
-            P.out_ld = mix_ld; P.out_scale = M.mix_scale;
+            P.out_ld = out_ld_now; P.out_scale = M.mix_scale;
             const dim3 cgrid(Tn, (ch + 127) / 128);
             ssd_conv_kernel<<<cgrid, 128, 0, st>>>(P, m->slots, conv, head);
             GlaArgs A;
@@ -2077,23 +2177,96 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.q_ld = A.k_ld = A.v_ld = ch;
             A.qk_share = M.heads / M.bc_groups;
             A.head_decay = head; A.head_step = head + (size_t)Tn * M.heads;
-            A.out_ld = mix_ld; A.out_scale = 1.0f;
+            A.out_ld = out_ld_now; A.out_scale = 1.0f;
             CU(launch_gla_scan_any(A, s->n_seqs, nullptr, m->slots, oraw, st));
             ssd_out_kernel<T><<<dim3(Tn, M.norm_parts), 256, 0, st>>>(P, oraw, conv, mix_at, m->slots);
             m->launches += 3;
             return SMOL_OK;
         };
+        // Mixers side by side that own their output projections keep their results apart: row stride = own columns.
+        const bool own_proj = L.side && L.proj_norm;
+        // Sigmoid attention over keys and values in the paged pool.
+        auto sigmoid_attention = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj, const float* bias, T* mix_at, int ld) -> int {
+            SigmoidArgs S;
+            AttnArgs& A = S.a;
+            A.proj = pj; A.n_in = n_in; A.bias = bias;
+            A.tok_seq = s->tok_seq; A.tok_pos = s->tok_pos; A.block_table = s->block_table;
+            A.max_pages = s->max_pages; A.page_size = c.page_size; A.n_pages = m->n_pages;
+            A.page_elems = m->page_elems; A.k_off = Ri.k_off; A.v_off = Ri.v_off;
+            A.H = M.heads; A.G = M.kv_heads; A.d = M.dim; A.dv = M.vdim; A.scale = M.score_scale; A.eps = c.norm_eps;
+            A.n_tokens = Tn; A.err = err; A.seq_start = s->seq_start;
+            A.k_ld = M.dim; A.v_ld = M.vdim; A.v_in_k = 0;
+            A.gate_off = (size_t)(M.heads + M.kv_heads) * M.dim; A.gate_ld = 1; A.gate_step = 0; A.has_gate = 1;
+            A.q_norm = A.k_norm = A.r1 = A.r2 = A.sink = A.slope = nullptr;
+            A.window = 0; A.softcap = A.two_over_cap = 0.0f;
+            A.split_len = A.n_splits = A.short_rows = 0; A.part = nullptr;
+            A.out_ld = ld; A.out_scale = 1.0f;
+            S.chunk = M.chunk; S.rot_pairs = M.rot_dims / 2; S.head_bias = M.head_bias; S.talk = M.talk;
+            S.freq = reinterpret_cast<const float*>(m->ws + m->o_freq) + Ri.freq_off;
+            const int units = Tn * (M.heads + M.kv_heads);
+            sigmoid_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(S, qbuf, pool);
+            const size_t smem = ((size_t)M.heads * (M.dim + 32) + (size_t)M.heads * M.heads) * sizeof(float);
+            if (M.vdim <= 256) sigmoid_attn_kernel<T, 8><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);
+            else sigmoid_attn_kernel<T, 16><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);
+            m->launches += 2;
+            return SMOL_OK;
+        };
+        // The scan's arguments for a linear attention with state [dim, vdim] per head in the slot.
+        auto scan_args = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj) {
+            GlaArgs A;
+            A.proj = pj; A.n_in = n_in; A.H = M.heads; A.d = M.dim; A.dv = M.vdim; A.rank = 0; A.n_tokens = Tn;
+            A.q_scale = 1.0f; A.tau = 1.0f; A.eps = c.norm_eps;
+            A.decay_w2 = A.decay_bias = A.out_norm = nullptr;
+            A.seq_start = s->seq_start; A.seq_pos0 = s->seq_pos0; A.seq_slot = s->seq_slot;
+            A.slot_floats = m->slot_floats; A.state_off = Ri.state_off; A.n_slots = m->n_slots; A.err = err;
+            A.qk_share = 1; A.head_decay = A.head_step = nullptr;
+            A.out_ld = M.heads * M.vdim; A.out_scale = 1.0f;
+            return A;
+        };
+        // Lightning attention: silu on q, k, v; the scan in its one-decay-per-head form; norm over all heads, sigmoid gate.
+        auto lightning = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj, T* mix_at, int ld) -> int {
+            const int hd = M.heads * M.dim, hv = M.heads * M.vdim, na = 2 * hd + hv;
+            LinPrepArgs P{pj, n_in, M.heads, M.dim, M.vdim, Tn, M.head_decay, nullptr, nullptr};
+            lightning_prep_kernel<<<dim3(Tn, (na + 1023) / 1024), 256, 0, st>>>(P, conv, head);
+            GlaArgs A = scan_args(M, Ri, pj);
+            A.q_src = conv; A.k_src = conv + hd; A.v_src = conv + 2 * hd;
+            A.q_ld = A.k_ld = A.v_ld = na;
+            A.head_decay = head; A.head_step = head + (size_t)Tn * M.heads;
+            CU(launch_gla_scan_any(A, s->n_seqs, nullptr, m->slots, oraw, st));
+            LinOutArgs O{pj, n_in, hv, hv, hv, 1, ld, (size_t)2 * hd + hv, c.norm_eps, 1.0f, M.out_norm};
+            lin_attn_out_kernel<T><<<dim3(Tn, 1), 256, 0, st>>>(O, oraw, mix_at);
+            m->launches += 3;
+            return SMOL_OK;
+        };
+        auto run_mixer = [&](const SmolLmLayer& M, const RunInfo& Ri, const float* pj, const float* bias, T* mix_at, int ld) -> int {
+            out_ld_now = ld;
+            if (M.mixer == SMOL_LM_MIX_SINK_ATTENTION) return attention(M, Ri, pj, bias, mix_at);
+            if (M.mixer == SMOL_LM_MIX_STATE_SPACE) return state_space(M, Ri, pj, bias, mix_at);
+            if (M.mixer == SMOL_LM_MIX_SIGMOID_ATTENTION) return sigmoid_attention(M, Ri, pj, bias, mix_at, ld);
+            return lightning(M, Ri, pj, mix_at, ld);
+        };
         if (pairable(L)) {
-            int rc = L.mixer == SMOL_LM_MIX_SINK_ATTENTION ? attention(L, R, proj, L.in_bias, mix) : state_space(L, R, proj, L.in_bias, mix);
+            int rc = run_mixer(L, R, proj, L.in_bias, mix, own_proj ? mix_cols_of(L) : mix_ld);
             if (rc == SMOL_OK && L.side) {
                 const SmolLmLayer& S = *L.side;
                 const float* sb = L.in_bias ? L.in_bias + n_in_main : nullptr;
-                T* at = mix + mix_cols_of(L);
-                rc = S.mixer == SMOL_LM_MIX_SINK_ATTENTION ? attention(S, m->side_runs[n], proj + n_in_main, sb, at)
-                                                           : state_space(S, m->side_runs[n], proj + n_in_main, sb, at);
+                rc = run_mixer(S, m->side_runs[n], proj + n_in_main, sb, own_proj ? mix2 : mix + mix_cols_of(L), own_proj ? mix_cols_of(S) : mix_ld);
             }
             if (rc != SMOL_OK) return rc;
-            mix_cols = mix_ld;
+            mix_cols = own_proj ? mix_cols_of(L) : mix_ld;
+        } else if (L.mixer == SMOL_LM_MIX_HGRN2) {
+            // q = silu(.), decay = the bounded forget gate, key = 1 - decay; norm per head, no gate
+            const int hd = L.heads * L.dim, hv = L.heads * L.vdim;
+            LinPrepArgs P{proj, n_in, L.heads, L.dim, L.vdim, Tn, nullptr, L.rate_bias, L.forget_lower};
+            hgrn2_prep_kernel<<<dim3(Tn, (hd + 1023) / 1024), 256, 0, st>>>(P, uk, auk, dec);
+            GlaArgs A = scan_args(L, R, proj);
+            A.q_src = uk; A.k_src = auk; A.v_src = proj + 2 * hd;
+            A.q_ld = A.k_ld = hd; A.v_ld = n_in;
+            CU(launch_gla_scan_any(A, s->n_seqs, dec, m->slots, oraw, st));
+            LinOutArgs O{proj, n_in, hv, L.vdim, L.vdim, 0, hv, 0, c.norm_eps, 1.0f, L.out_norm};
+            lin_attn_out_kernel<T><<<dim3(Tn, L.heads), 128, 0, st>>>(O, oraw, mix);
+            m->launches += 3;
+            mix_cols = hv;
         } else if (L.mixer == SMOL_LM_MIX_LATENT_ATTENTION) {
             AttnArgs A;
             A.proj = proj; A.n_in = n_in; A.bias = nullptr;
@@ -2176,13 +2349,16 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             mix_cols = L.heads * L.dim;
         }
         CU(linear<T>(m, mix_in, static_cast<const T*>(L.w_out), y, Tn, D, mix_cols, st));
+        if (own_proj) CU(linear<T>(m, mix2, static_cast<const T*>(L.side->w_out), y2, Tn, D, mix_cols_of(*L.side), st));
         const bool last = n + 1 == m->runs.size();
         const float* next_norm1 = last ? nullptr : m->layers[m->runs[n + 1].layer].norm1;
         // the feed-forward reads hn and leaves its output in y (routed experts under the post-norm block: in `routed`)
         RoutedSum routed;
         routed.yp = nullptr; routed.slot_of = nullptr; routed.sel_w = nullptr; routed.top = 0;
         const RoutedSum no_sum = routed;
-        auto actp_of = [](const SmolLmLayer& M) { return ActParams{M.mlp_act, M.act_limit, M.act_alpha}; };
+        auto actp_of = [](const SmolLmLayer& M) { return ActParams{M.mlp_act, M.act_limit, M.act_alpha, 0}; };
+        // the experts (and a shared expert) of a routed feed-forward may lack gate rows
+        auto expert_actp = [](const SmolLmLayer& M) { return ActParams{M.mlp_act, M.act_limit, M.act_alpha, M.ff_plain ? 1 : 0}; };
         auto feed_forward = [&]() -> int {
             if (L.mlp == SMOL_LM_MLP_POLYNORM) {
                 CU(linear<T>(m, hn, static_cast<const T*>(L.w_up), z, Tn, L.ff, D, st));
@@ -2209,7 +2385,7 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 RouteArgs Rt;
                 Rt.w_router = L.w_router; Rt.bias = L.route_bias; Rt.D = D; Rt.E = L.n_experts + L.n_identity; Rt.E_real = L.n_experts;
                 Rt.top = L.top_k; Rt.n_groups = L.n_groups; Rt.keep = L.keep_groups; Rt.scale = L.router_scale; Rt.n_tokens = Tn;
-                Rt.score = L.router_score; Rt.plain = L.router_plain;
+                Rt.score = L.router_score; Rt.plain = L.router_plain; Rt.group_top = L.group_rank_top;
                 const int pairs = Tn * L.top_k;
                 // the router reads the sublayer's input in fp32 where the block keeps it (post-norm), else its T form
                 float* r_logits = reinterpret_cast<float*>(m->ws + m->o_rlogits);
@@ -2221,14 +2397,15 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 if (L.n_experts > 0) {
                     // three forms of the two grouped products, by how many rows an expert gets: a warp per output column for
                     // a handful of pairs (decoding), 32-row mma.sync tiles, 128-row tcgen05 tiles over rows copied into sorted order
+                    const int NF = L.ff_plain ? L.ff : 2 * L.ff;          // rows of an expert's first matrix
                     const bool few = !kIsF32 && pairs <= kMoeGemvPairs && D % 8 == 0 && L.ff % 8 == 0;
                     const bool big = !kIsF32 && !few && m->tc_ready && pairs / L.n_experts >= 64 && D % 8 == 0 && L.ff % 8 == 0 &&
-                                     2 * L.ff >= kTcTileN && D >= kTcTileN && D >= smol::umma::kBK && L.ff >= smol::umma::kBK;
+                                     NF >= kTcTileN && D >= kTcTileN && D >= smol::umma::kBK && L.ff >= smol::umma::kBK;
                     const int tile_rows = big ? smol::umma::kM : kGroupTile;
                     moe_index_kernel<<<1, 256, 0, st>>>(sel_id, pairs, L.n_experts, tile_rows, seg, perm, slot_of, tile_g, tile_r, n_tiles);
                     const int tiles = pairs / kGroupTile + L.n_experts;
-                    GemmIo io = plain_io(D, 2 * L.ff);
-                    io.sw = (long long)2 * L.ff * D;
+                    GemmIo io = plain_io(D, NF);
+                    io.sw = (long long)NF * D;
                     io.tile_group = tile_g; io.tile_row0 = tile_r; io.seg = seg; io.n_tiles = n_tiles;
                     GemmIo io2 = plain_io(L.ff, D);
                     io2.sw = (long long)D * L.ff;
@@ -2242,12 +2419,12 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                         m->launches++;
                     }
                     if (few) {
-                        moe_gemv_kernel<false><<<dim3((2 * L.ff + 7) / 8, pairs), 256, 0, st>>>(L.route_input ? ap : hn, perm, L.route_input ? 0 : L.top_k, sel_id,
-                                                                                               seg + L.n_experts, reinterpret_cast<const bf16*>(L.w_experts_in), io.sw,
-                                                                                               zp, 2 * L.ff, D, actp_of(L));
+                        moe_gemv_kernel<false><<<dim3((NF + 7) / 8, pairs), 256, 0, st>>>(L.route_input ? ap : hn, perm, L.route_input ? 0 : L.top_k, sel_id,
+                                                                                         seg + L.n_experts, reinterpret_cast<const bf16*>(L.w_experts_in), io.sw,
+                                                                                         zp, NF, D, expert_actp(L));
                         // the second product applies the activation as it reads the first one's result
                         moe_gemv_kernel<true><<<dim3((D + 7) / 8, pairs), 256, 0, st>>>(zp, perm, 0, sel_id, seg + L.n_experts,
-                                                                                        reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff, actp_of(L));
+                                                                                        reinterpret_cast<const bf16*>(L.w_experts_out), io2.sw, yp, D, L.ff, expert_actp(L));
                         m->launches += 1;
                     } else {
                         bool done = false;
@@ -2258,13 +2435,13 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                                 m->launches++;
                             }
                             done = linear_grouped_tc(m, reinterpret_cast<const bf16*>(ap), reinterpret_cast<const bf16*>(L.w_experts_in), zp, pairs, L.n_experts,
-                                                     2 * L.ff, D, io, st);
+                                                     NF, D, io, st);
                         }
                         if (!done) {
                             if (!L.route_input) { io.gather = perm; io.gather_div = L.top_k; }
-                            CU(linear_ex<T>(m, L.route_input ? ap : hn, static_cast<const T*>(L.w_experts_in), zp, pairs, 2 * L.ff, D, io, 1, tiles, st));
+                            CU(linear_ex<T>(m, L.route_input ? ap : hn, static_cast<const T*>(L.w_experts_in), zp, pairs, NF, D, io, 1, tiles, st));
                         }
-                        gated_act_kernel<T><<<cast_grid(act_n / 4), 256, 0, st>>>(zp, L.ff, actp_of(L), (size_t)pairs, actp);
+                        gated_act_kernel<T><<<cast_grid(act_n / 4), 256, 0, st>>>(zp, L.ff, expert_actp(L), (size_t)pairs, actp);
                         if (!(big && linear_grouped_tc(m, reinterpret_cast<const bf16*>(actp), reinterpret_cast<const bf16*>(L.w_experts_out), yp, pairs,
                                                        L.n_experts, D, L.ff, io2, st)))
                             CU(linear_ex<T>(m, actp, static_cast<const T*>(L.w_experts_out), yp, pairs, D, L.ff, io2, 1, tiles, st));
@@ -2273,12 +2450,49 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
                 } else {
                     CU(cudaMemsetAsync(slot_of, 0xff, (size_t)pairs * 4, st));
                 }
+                if (L.shared_ff > 0) {
+                    // the expert every token uses: its result lands in y and joins the routed sum in the kernel that follows
+                    const int SF = L.ff_plain ? L.shared_ff : 2 * L.shared_ff;
+                    CU(linear<T>(m, hn, static_cast<const T*>(L.w_shared_in), z, Tn, SF, D, st));
+                    gated_act_kernel<T><<<cast_grid((size_t)Tn * L.shared_ff / 4), 256, 0, st>>>(z, L.shared_ff, expert_actp(L), (size_t)Tn, act);
+                    CU(linear<T>(m, act, static_cast<const T*>(L.w_shared_out), y, Tn, D, L.shared_ff, st));
+                    m->launches += 1;
+                }
                 // summed by the norm that follows
                 routed.yp = yp; routed.slot_of = slot_of; routed.sel_w = L.route_input ? nullptr : sel_w; routed.top = L.top_k;
             }
             return SMOL_OK;
         };
-        if (postnorm) {
+        if (prenorm) {
+            // x += mixer (mixers with their own projections: each normed over the width first); x += feed-forward.  The kernel
+            // that ends the layer also leaves the traced row, restarts the stream where the next run asks for it and applies
+            // the next layer's first norm.
+            const bool has_ff = L.mlp != SMOL_LM_MLP_NONE;
+            const SmolLmLayer* Ln = last ? nullptr : &m->layers[m->runs[n + 1].layer];
+            const NormSpec after = Ln ? norm_of(Ln->norm1, Ln->norm1_shift, Ln->norm1_alpha) : no_norm;
+            const float* restart = (!last && (m->runs[n + 1].flags & SMOL_LM_RUN_ADD_EMBED)) ? x0 : nullptr;
+            float* tr_row = s->trace ? s->trace + n * (size_t)Tn * D : nullptr;
+            ResidualArgs Ra;
+            Ra.x = x; Ra.D = D; Ra.eps = c.norm_eps;
+            Ra.y = y; Ra.y_w = own_proj ? L.proj_norm : nullptr; Ra.sy = own_proj ? L.mix_scale : 1.0f;
+            Ra.y2 = own_proj ? y2 : nullptr; Ra.y2_w = own_proj ? L.side->proj_norm : nullptr; Ra.sy2 = own_proj ? L.side->mix_scale : 0.0f;
+            Ra.rs = no_sum;
+            Ra.trace = has_ff ? nullptr : tr_row; Ra.x0 = has_ff ? nullptr : restart;
+            Ra.next = has_ff ? norm_of(L.norm2, L.norm2_shift, L.norm2_alpha) : after;
+            residual_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(Ra, hn, hn);
+            m->launches += 1;
+            if (has_ff) {
+                const int rc = feed_forward();
+                if (rc != SMOL_OK) return rc;
+                const bool summed = routed.yp != nullptr;
+                Ra.y = (!summed || L.shared_ff > 0) ? y : nullptr; Ra.y_w = nullptr; Ra.sy = 1.0f;
+                Ra.y2 = nullptr; Ra.y2_w = nullptr; Ra.sy2 = 0.0f;
+                Ra.rs = routed;
+                Ra.trace = tr_row; Ra.x0 = restart; Ra.next = after;
+                residual_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(Ra, hn, hn);
+                m->launches += 1;
+            }
+        } else if (postnorm) {
             // x <- g1 * rms_divide(alpha x + mixer); x <- g2 * rms_divide(alpha x + ff); the layer's result joins the history
             // and the stream becomes the weighted sum of the history
             const bool has_ff = L.mlp != SMOL_LM_MLP_NONE;
@@ -2302,11 +2516,12 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             add_norm_kernel<T><<<Tn, nthr, D * sizeof(float), st>>>(x, y, L.norm1b, L.ls1, next_norm1, c.norm_eps, D, hn, woff, L.out_bias, no_sum, hn);
             m->launches += 1;
         }
-        if (s->trace) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));
+        if (s->trace && !prenorm) CU(cudaMemcpyAsync(s->trace + n * (size_t)Tn * D, x, (size_t)Tn * D * 4, cudaMemcpyDeviceToDevice, st));
     }
     if (s->n_want > 0) {
         if (postnorm) post_norm_kernel<T><<<s->n_want, nthr, 2 * D * sizeof(float), st>>>(x, nullptr, c.logit_scale, m->g.final_norm, c.norm_eps, D, nullptr, 0, 0,
                                                                                       nullptr, s->want_rows, hw, RoutedSum{nullptr, nullptr, nullptr, 0});
+        else if (prenorm) prenorm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, norm_of(m->g.final_norm, m->g.final_norm_shift, m->g.final_norm_alpha), D, hw);
         else norm_rows_kernel<T><<<s->n_want, nthr, 0, st>>>(x, s->want_rows, m->g.final_norm, c.norm_eps, D, hw, woff);
         m->launches++;
         CU(linear<T>(m, hw, static_cast<const T*>(m->g.head), s->logits, s->n_want, c.vocab, D, st));

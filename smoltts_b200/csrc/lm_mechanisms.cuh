@@ -17,14 +17,24 @@ __device__ __forceinline__ float gelu_tanh_(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 __device__ __forceinline__ float silu_(float z) { return z * sigmoidf_(z); }
-__device__ __forceinline__ float gated_act_(int kind, float z) { return kind == SMOL_LM_ACT_SILU ? silu_(z) : gelu_tanh_(z); }
+__device__ __forceinline__ float gated_act_(int kind, float z) {
+    if (kind == SMOL_LM_ACT_SILU) return silu_(z);
+    if (kind == SMOL_LM_ACT_RELU_SQUARED) {
+        const float r = fmaxf(z, 0.0f);
+        return r * r;
+    }
+    return gelu_tanh_(z);
+}
 // A gated unit's value from its gate and up inputs.  SMOL_LM_ACT_CLAMPED: g = min(gate, limit), u = clamp(up, -limit, limit),
-// g * sigmoid(alpha * g) * (u + 1); the other kinds: act(gate) * up.
+// g * sigmoid(alpha * g) * (u + 1); the other kinds: act(gate) * up.  `plain`: the unit has no gate rows -- a row of the
+// first product holds F values (not 2 F) and the unit's value is act(value).
 struct ActParams {
     int kind;
     float limit, alpha;
+    int plain;
 };
 __device__ __forceinline__ float gated_unit_(const ActParams& a, float g, float u) {
+    if (a.plain) return gated_act_(a.kind, g);
     if (a.kind == SMOL_LM_ACT_CLAMPED) {
         g = fminf(g, a.limit);
         u = fminf(fmaxf(u, -a.limit), a.limit);
@@ -643,11 +653,12 @@ __global__ void ssd_out_kernel(const SsdArgs A, const float* __restrict__ o_raw,
 // Gated feed-forward: z rows hold gate [F] | up [F]; out = the gated unit's value (act(gate) * up, or the clamped form) in T.
 template <class T>
 __global__ void gated_act_kernel(const float* __restrict__ z, int F, const ActParams kind, size_t rows, T* __restrict__ out) {
+    const size_t ld = kind.plain ? F : 2 * F, uo = kind.plain ? 0 : F;      // plain: the "up" operand is the value itself, unused
     if (F % 4 == 0) {                      // 16-byte pieces
         const size_t n = rows * (F / 4);
         for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
             const size_t r = i / (F / 4), c = (i - r * (F / 4)) * 4;
-            const float4 g = *reinterpret_cast<const float4*>(z + r * 2 * F + c), u = *reinterpret_cast<const float4*>(z + r * 2 * F + F + c);
+            const float4 g = *reinterpret_cast<const float4*>(z + r * ld + c), u = *reinterpret_cast<const float4*>(z + r * ld + uo + c);
             store4<T>(out + r * F + c, gated_unit_(kind, g.x, u.x), gated_unit_(kind, g.y, u.y), gated_unit_(kind, g.z, u.z),
                       gated_unit_(kind, g.w, u.w));
         }
@@ -656,7 +667,7 @@ __global__ void gated_act_kernel(const float* __restrict__ z, int F, const ActPa
     const size_t n = rows * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / F, c = i - r * F;
-        out[i] = from_f<T>(gated_unit_(kind, z[r * 2 * F + c], z[r * 2 * F + F + c]));
+        out[i] = from_f<T>(gated_unit_(kind, z[r * ld + c], z[r * ld + uo + c]));
     }
 }
 
@@ -669,6 +680,7 @@ struct RouteArgs {
     int n_tokens;
     int score;        // SMOL_LM_ROUTE_*: softmax over the outputs, or a sigmoid of each
     int plain;        // 1: a chosen output's weight is its score (times scale), not divided by the chosen scores' sum
+    int group_top;    // a group is ranked by the sum of its group_top best choice scores (at most 1: by its best)
 };
 constexpr int kMaxRouted = 1024;       // router outputs (experts + identity outputs)
 constexpr int kMaxTop = 32;
@@ -743,7 +755,17 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const RouteArgs A, const
     if (A.keep < A.n_groups) {
         for (int g = threadIdx.x; g < A.n_groups; g += blockDim.x) {
             float gs = -INFINITY;
-            for (int e = g * size; e < (g + 1) * size; ++e) gs = fmaxf(gs, choice[e]);
+            if (A.group_top <= 1) {
+                for (int e = g * size; e < (g + 1) * size; ++e) gs = fmaxf(gs, choice[e]);
+            } else {
+                // the scores that fewer than group_top others of the group beat (ties: the lower index first), in index order
+                gs = 0.0f;
+                for (int e = g * size; e < (g + 1) * size; ++e) {
+                    int better = 0;
+                    for (int f = g * size; f < (g + 1) * size; ++f) better += (choice[f] > choice[e] || (choice[f] == choice[e] && f < e)) ? 1 : 0;
+                    if (better < A.group_top) gs += choice[e];
+                }
+            }
             gscore[g] = gs;
         }
         __syncthreads();
@@ -866,11 +888,12 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const void* __restrict__ 
     const bf16* wr = w + (long long)sel_id[pair] * w_stride + (size_t)n * K;
     float acc = 0.0f;
     if (ACT) {
-        const float* zr = static_cast<const float*>(a_any) + (size_t)r * 2 * K;
+        const float* zr = static_cast<const float*>(a_any) + (size_t)r * (act.plain ? K : 2 * K);
+        const int uo = act.plain ? 0 : K;
         for (int k = lane * 8; k < K; k += 256) {
             const uint4 wv = ldg_stream(wr + k);
             const float4 g0 = *reinterpret_cast<const float4*>(zr + k), g1 = *reinterpret_cast<const float4*>(zr + k + 4);
-            const float4 u0 = *reinterpret_cast<const float4*>(zr + K + k), u1 = *reinterpret_cast<const float4*>(zr + K + k + 4);
+            const float4 u0 = *reinterpret_cast<const float4*>(zr + uo + k), u1 = *reinterpret_cast<const float4*>(zr + uo + k + 4);
             acc = fmaf(bf16_round(gated_unit_(act, g0.x, u0.x)), bf_lo(wv.x), acc); acc = fmaf(bf16_round(gated_unit_(act, g0.y, u0.y)), bf_hi(wv.x), acc);
             acc = fmaf(bf16_round(gated_unit_(act, g0.z, u0.z)), bf_lo(wv.y), acc); acc = fmaf(bf16_round(gated_unit_(act, g0.w, u0.w)), bf_hi(wv.y), acc);
             acc = fmaf(bf16_round(gated_unit_(act, g1.x, u1.x)), bf_lo(wv.z), acc); acc = fmaf(bf16_round(gated_unit_(act, g1.y, u1.y)), bf_hi(wv.z), acc);

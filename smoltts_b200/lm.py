@@ -10,6 +10,10 @@ pool) or a gated linear recurrence (state per head in the slot); gated feed-forw
 ``SunutarLM`` serves the Sunutar design: sandwich layers whose mixer is a pair on the same input -- windowed attention
 (keys and values in the paged pool) beside a state-space recurrence (state and convolution inputs in the slot) -- with
 clamped gated feed-forwards, dense or routed by sigmoid scores; the logits reuse the embedding table.
+``GuniraxLM`` serves the Gunirax design: pre-norm layers with Dynamic-Tanh norms, a looped span of layers whose later
+passes restart from stream + embedding output; mixers are a pair -- chunked sigmoid attention with mixed heads (keys and
+values in the paged pool) beside lightning attention (state in the slot), each projected and normed on its own -- or
+HGRN2; feed-forwards are gated or routed squared-relu experts with a shared expert.
 
 The engine owns two pools -- key/value pages (``PagePool``) and state slots (``SlotPool``) -- and one step function,
 ``forward``: any number of sequences, each with its next tokens (a portion of a prompt or a single decoded token).
@@ -30,8 +34,8 @@ import torch
 
 from . import _capi_lm
 from ._errors import SMOL_ERR_CAPACITY, SmolError
-from .lm_config import (ACT_CLAMPED, ACT_GELU_TANH, ACT_SILU, BLOCK_POSTNORM, BLOCK_SANDWICH, MAFERAX_MLP_KINDS, MIXER_KINDS, MLP_KINDS,
-                        ROUTE_SIGMOID, MaferaxConfig, PamasunConfig, SunutarConfig)
+from .lm_config import (ACT_CLAMPED, ACT_GELU_TANH, ACT_RELU_SQUARED, ACT_SILU, BLOCK_POSTNORM, BLOCK_PRENORM, BLOCK_SANDWICH, MAFERAX_MLP_KINDS,
+                        MIXER_KINDS, MLP_KINDS, NORM_DYT, ROUTE_SIGMOID, GuniraxConfig, MaferaxConfig, PamasunConfig, SunutarConfig)
 from .pool import PagePool, SlotPool
 
 _ST_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "I32": torch.int32, "I64": torch.int64}
@@ -154,6 +158,10 @@ class HybridLM:
         for k, v in desc["config"].items():
             setattr(ccfg, k, v)
         runs = (C.c_int32 * len(self.runs))(*self.runs)
+        flags = desc.get("run_flags")
+        if flags is not None:
+            run_flags = (C.c_int32 * len(self.runs))(*flags)          # stays alive until create has copied it
+            ccfg.run_flags = C.cast(run_flags, C.POINTER(C.c_int32))
         if self._h:
             self.lib.smol_lm_destroy(self._h)
         h = C.c_void_p()
@@ -470,3 +478,75 @@ class SunutarLM(HybridLM):
                 c.w_router = vec(p + "mlp.router").data_ptr()
         embed = mat("embed")
         return {"config": {"norm_plain": 1}, "globals": {"embed": embed, "head": embed, "final_norm": vec("final.norm")}}
+
+
+class GuniraxLM(HybridLM):
+    """B200 engine of one Gunirax checkpoint."""
+
+    architecture = "Gunirax"
+    config_class = GuniraxConfig
+
+    def _shapes(self, sd):
+        return self.config.tensor_shapes()
+
+    def _describe(self, sd, layers, mat, vec):
+        cfg = self.config
+        self._sides = []                                   # the side mixers' structs live as long as the engine's create call needs them
+
+        def norm(c, field, name):
+            setattr(c, field, vec(name).data_ptr())
+            setattr(c, field + "_shift", vec(name + ".b").data_ptr())
+            setattr(c, field + "_alpha", vec(name + ".alpha").data_ptr())
+
+        for i, L in enumerate(cfg.layers):
+            p, c = f"l{i}.", layers[i]
+            norm(c, "norm1", p + "norm1")
+            if L.kind == "parallel":
+                a, r, q, t = L.left, L.right, p + "mix.left.", p + "mix.right."
+                # the sigmoid attention is the layer's own mixer, the lightning attention its side mixer: one input product,
+                # then each its own output product, a norm over the width and half the weight
+                c.mixer, c.heads, c.kv_heads, c.dim, c.vdim = MIXER_KINDS["sigmoid_attention"], a.heads, a.kv_heads, a.dim, a.vdim
+                c.score_scale, c.chunk, c.mix_scale = a.scale, a.chunk, 0.5
+                c.rot_dims, c.rot_base = a.rot.dims, a.rot.base
+                c.rot_stretch, c.rot_low, c.rot_high, c.rot_original = a.rot.factor, a.rot.low, a.rot.high, a.rot.original
+                c.head_bias, c.talk = vec(q + "pb").data_ptr(), vec(q + "talk").data_ptr()
+                c.w_in = mat(q + "q", q + "k", q + "g", t + "q", t + "k", t + "v", t + "g").data_ptr()
+                n_right = 2 * r.heads * r.dim + 2 * r.heads * r.vdim
+                c.in_bias = vec(torch.cat([sd[q + "q.b"].float(), sd[q + "k.b"].float(), torch.zeros(a.heads + n_right)])).data_ptr()
+                c.w_out, c.proj_norm = mat(q + "o").data_ptr(), vec(p + "mix.left.out").data_ptr()
+                side = _capi_lm.SmolLmLayer()
+                side.mixer, side.heads, side.kv_heads, side.dim, side.vdim = MIXER_KINDS["lightning"], r.heads, r.heads, r.dim, r.vdim
+                side.mix_scale = 0.5
+                side.head_decay = vec(torch.tensor(r.decay, dtype=torch.float32)).data_ptr()
+                side.out_norm = vec(t + "norm").data_ptr()
+                side.w_out, side.proj_norm = mat(t + "o").data_ptr(), vec(p + "mix.right.out").data_ptr()
+                self._sides.append(side)
+                c.side = C.pointer(side)
+            else:
+                m, q = L.mixer, p + "mix."
+                c.mixer, c.heads, c.kv_heads, c.dim, c.vdim = MIXER_KINDS["hgrn2"], m.heads, m.heads, m.dim, m.vdim
+                c.w_in = mat(q + "q", q + "f", q + "v").data_ptr()
+                c.rate_bias, c.forget_lower, c.out_norm = vec(q + "f.b").data_ptr(), vec(q + "lower").data_ptr(), vec(q + "norm").data_ptr()
+                c.w_out = mat(q + "o").data_ptr()
+            c.mlp = MAFERAX_MLP_KINDS[L.mlp_kind]          # none / gated / routed experts
+            if L.mlp_kind:
+                norm(c, "norm2", p + "norm2")
+                c.ff = L.ff
+            if L.mlp_kind == "dense":
+                c.mlp_act = ACT_SILU
+                c.w_up, c.w_down = mat(p + "mlp.gate", p + "mlp.up").data_ptr(), mat(p + "mlp.down").data_ptr()
+            elif L.mlp_kind == "moe":
+                r = L.router
+                c.mlp_act, c.ff_plain = ACT_RELU_SQUARED, 1
+                c.n_experts, c.n_identity, c.top_k, c.n_groups, c.keep_groups, c.router_scale = r.experts, 0, r.top, r.groups, r.keep, r.scale
+                c.router_score, c.group_rank_top = ROUTE_SIGMOID, L.group_score_top
+                c.w_experts_in = mat(*[f"{p}mlp.e{e}.up" for e in range(r.experts)]).data_ptr()
+                c.w_experts_out = mat(*[f"{p}mlp.e{e}.down" for e in range(r.experts)]).data_ptr()
+                c.w_router, c.route_bias = vec(p + "mlp.router").data_ptr(), vec(p + "mlp.correction").data_ptr()
+                if L.shared_ff:
+                    c.shared_ff = L.shared_ff
+                    c.w_shared_in, c.w_shared_out = mat(p + "mlp.shared.up").data_ptr(), mat(p + "mlp.shared.down").data_ptr()
+        return {"config": {"block": BLOCK_PRENORM, "norm_kind": NORM_DYT, "embed_scale": cfg.embedding_scale},
+                "run_flags": cfg.run_restarts(),
+                "globals": {"embed": mat("embed"), "head": mat("head"), "final_norm": vec("final.norm"),
+                            "final_norm_shift": vec("final.norm.b"), "final_norm_alpha": vec("final.norm.alpha")}}

@@ -22,6 +22,7 @@ register_model("dual_ar", "smoltts_b200.model", "RQTransformer")
 register_model("Pamasun", "smoltts_b200.lm", "PamasunLM")
 register_model("Maferax", "smoltts_b200.lm", "MaferaxLM")
 register_model("Sunutar", "smoltts_b200.lm", "SunutarLM")
+register_model("Gunirax", "smoltts_b200.lm", "GuniraxLM")
 
 
 def registered() -> Dict[str, Tuple[str, str]]:
