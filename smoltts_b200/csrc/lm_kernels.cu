@@ -1830,6 +1830,13 @@ static cudaError_t scan_attribute() {
 }
 static constexpr int flash_smem_bytes(int DK, int DV, bool vk) { return 2 * 64 * ((DK + 8) + (vk ? 0 : DV + 8)) * (int)sizeof(bf16); }
 
+template <int DK, int HPW>
+static cudaError_t sigmoid_flash_attributes() {
+    cudaError_t e = cudaFuncSetAttribute(sigmoid_flash_kernel<DK, HPW, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_flash_kernel<DK, HPW, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    return e;
+}
+
 template <class T>
 static cudaError_t set_kernel_attributes() {
     cudaError_t e = scan_attribute<16>();
@@ -1841,6 +1848,12 @@ static cudaError_t set_kernel_attributes() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_attn_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_attn_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = sigmoid_flash_attributes<32, 1>();
+    if (e == cudaSuccess) e = sigmoid_flash_attributes<64, 1>();
+    if (e == cudaSuccess) e = sigmoid_flash_attributes<96, 1>();
+    if (e == cudaSuccess) e = sigmoid_flash_attributes<128, 1>();
+    if (e == cudaSuccess) e = sigmoid_flash_attributes<32, 2>();
+    if (e == cudaSuccess) e = sigmoid_flash_attributes<64, 2>();
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<128, 128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(128, 128, false));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<192, 128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(192, 128, true));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_flash_kernel<192, 192, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, flash_smem_bytes(192, 192, true));
@@ -2072,6 +2085,48 @@ static void launch_attention(SmolLm* m, const SmolLmStep* s, AttnArgs& A, bool f
     }
 }
 
+// The tiled sigmoid attention over the sequences that bring more than kShortSeq tokens.  Returns false where this form does
+// not apply (fp32 engine, sizes it is not built for, unaligned cached rows, more shared memory than an SM has): the caller
+// then runs the warp-per-head kernel over every row.
+constexpr int kSigmoidSmemMax = 200 * 1024;
+static size_t sigmoid_flash_smem(int H, int G, int DK, int KT) {
+    return (size_t)2 * G * KT * (DK + 8) * sizeof(bf16) + ((size_t)H * 16 * (KT + 8) + (size_t)H * H) * sizeof(float);
+}
+template <int DK, int HPW>
+static bool launch_sigmoid_flash_sized(const SigmoidArgs& S, dim3 grid, int threads, const bf16* qbuf, const bf16* pool, bf16* out, cudaStream_t st) {
+    const AttnArgs& A = S.a;
+    if (sigmoid_flash_smem(A.H, A.G, DK, 64) <= (size_t)kSigmoidSmemMax) {
+        sigmoid_flash_kernel<DK, HPW, 64><<<grid, threads, sigmoid_flash_smem(A.H, A.G, DK, 64), st>>>(S, qbuf, pool, out);
+        return true;
+    }
+    if (sigmoid_flash_smem(A.H, A.G, DK, 32) <= (size_t)kSigmoidSmemMax) {
+        sigmoid_flash_kernel<DK, HPW, 32><<<grid, threads, sigmoid_flash_smem(A.H, A.G, DK, 32), st>>>(S, qbuf, pool, out);
+        return true;
+    }
+    return false;
+}
+static bool launch_sigmoid_flash(SmolLm* m, const SmolLmStep* s, const SigmoidArgs& S, int max_n, const bf16* qbuf, const bf16* pool, bf16* out,
+                                 bool is_bf16, cudaStream_t st) {
+    const AttnArgs& A = S.a;
+    if (!is_bf16 || A.d % 8 != 0 || A.d > 128 || A.k_off % 8 != 0 || A.v_off % 8 != 0) return false;
+    const dim3 grid((max_n + 15) / 16, s->n_seqs);
+    bool done;
+    if (A.H <= 16) {
+        const int threads = A.H * 32;
+        if (A.d <= 32) done = launch_sigmoid_flash_sized<32, 1>(S, grid, threads, qbuf, pool, out, st);
+        else if (A.d <= 64) done = launch_sigmoid_flash_sized<64, 1>(S, grid, threads, qbuf, pool, out, st);
+        else if (A.d <= 96) done = launch_sigmoid_flash_sized<96, 1>(S, grid, threads, qbuf, pool, out, st);
+        else done = launch_sigmoid_flash_sized<128, 1>(S, grid, threads, qbuf, pool, out, st);
+    } else {
+        const int threads = (A.H + 1) / 2 * 32;
+        if (A.d <= 32) done = launch_sigmoid_flash_sized<32, 2>(S, grid, threads, qbuf, pool, out, st);
+        else if (A.d <= 64) done = launch_sigmoid_flash_sized<64, 2>(S, grid, threads, qbuf, pool, out, st);
+        else done = false;
+    }
+    if (done) m->launches += 1;
+    return done;
+}
+
 template <class T>
 static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
     const SmolLmConfig& c = m->cfg;
@@ -2201,14 +2256,23 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.window = 0; A.softcap = A.two_over_cap = 0.0f;
             A.split_len = A.n_splits = A.short_rows = 0; A.part = nullptr;
             A.out_ld = ld; A.out_scale = 1.0f;
-            S.chunk = M.chunk; S.rot_pairs = M.rot_dims / 2; S.head_bias = M.head_bias; S.talk = M.talk;
+            S.chunk = M.chunk; S.rot_pairs = M.rot_dims / 2; S.head_bias = M.head_bias; S.talk = M.talk; S.skip_long = 0;
             S.freq = reinterpret_cast<const float*>(m->ws + m->o_freq) + Ri.freq_off;
             const int units = Tn * (M.heads + M.kv_heads);
             sigmoid_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(S, qbuf, pool);
-            const size_t smem = ((size_t)M.heads * (M.dim + 32) + (size_t)M.heads * M.heads) * sizeof(float);
-            if (M.vdim <= 256) sigmoid_attn_kernel<T, 8><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);
-            else sigmoid_attn_kernel<T, 16><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);
-            m->launches += 2;
+            m->launches += 1;
+            const int min_n = s->min_seq_tokens > 0 ? s->min_seq_tokens : 1;
+            const int max_n = s->max_seq_tokens > 0 ? s->max_seq_tokens : Tn;
+            // sequences that bring more than a few tokens take the tiled tensor-core form (bf16), the others a warp per head
+            const bool tiled = max_n > kShortSeq && launch_sigmoid_flash(m, s, S, max_n, reinterpret_cast<const bf16*>(qbuf), reinterpret_cast<const bf16*>(pool),
+                                                                         reinterpret_cast<bf16*>(mix_at), sizeof(T) == 2, st);
+            if (!tiled || min_n <= kShortSeq) {
+                S.skip_long = tiled ? 1 : 0;
+                const size_t smem = ((size_t)M.heads * (M.dim + 32) + (size_t)M.heads * M.heads) * sizeof(float);
+                if (M.vdim <= 256) sigmoid_attn_kernel<T, 8><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);
+                else sigmoid_attn_kernel<T, 16><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);
+                m->launches += 1;
+            }
             return SMOL_OK;
         };
         // The scan's arguments for a linear attention with state [dim, vdim] per head in the slot.

@@ -139,6 +139,7 @@ struct SigmoidArgs {
     int rot_pairs;                 // leading pairs (2i, 2i+1) of a head that are rotated
     const float* freq;             // [rot_pairs]
     const float *head_bias, *talk; // [H], [H][H]
+    int skip_long;                 // 1: the warp-per-head kernel leaves sequences of more than kShortSeq tokens to the tiled kernel
 };
 __device__ __forceinline__ int sigmoid_first_key(const SigmoidArgs& S, int pos) { return S.chunk > 0 ? pos / S.chunk * S.chunk : 0; }
 
@@ -211,6 +212,10 @@ __global__ void __launch_bounds__(kSigmoidMaxHeads * 32) sigmoid_attn_kernel(con
     const AttnArgs& A = S.a;
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, H = A.H;
     const int t = blockIdx.x;
+    if (S.skip_long) {
+        const int sq = A.tok_seq[t];
+        if (A.seq_start[sq + 1] - A.seq_start[sq] > kShortSeq) return;
+    }
     const int g = h / (H / A.G);
     float* qs = sig_smem + h * A.d;
     float* ws = sig_smem + H * A.d;
@@ -254,6 +259,160 @@ __global__ void __launch_bounds__(kSigmoidMaxHeads * 32) sigmoid_attn_kernel(con
     for (int e = 0; e < MAXV; ++e) {
         const int c = lane + e * 32;
         if (c < A.dv) out[(size_t)t * A.out_ld + h * A.dv + c] = from_f<T>(o[e] * attn_gate(A, t, h, c));
+    }
+}
+
+// Sigmoid attention for prompt portions, bf16, on the tensor cores (mma.sync m16n8k16, fp32 accumulation).  One block per
+// (16-row tile of a sequence's rows in this step, sequence); warp w owns the heads w, w + warps, ... (HPW of them at most).
+// Keys and values of every key/value head are staged KT absolute positions at a time.  Per tile, in two phases:
+//   1. every warp scores its heads' queries against the tile (Q K^T on the tensor cores), turns the scores into
+//      sigmoid(score * scale + bias_h), zero outside the mask, and leaves them in shared memory in fp32;
+//   2. after a barrier every warp mixes, for each of its heads, the H weight maps with its row of the mixing matrix (fp32
+//      FMAs on the fragment it is about to feed), splits the result into a bf16 head and a bf16 remainder (16 mantissa bits
+//      kept) and adds weights x values on the tensor cores.
+// Masked keys weigh exactly zero, and tiles are absolute positions, so a row's sum does not depend on how the step was cut.
+// The sigmoid uses the hardware exponential and division (relative error about 2^-21; this form serves bf16 only).
+// Needs d % 8 == 0 and 16-byte aligned cached rows.
+template <int DK, int HPW, int KT>
+__global__ void __launch_bounds__(HPW == 1 ? 512 : 256) sigmoid_flash_kernel(const SigmoidArgs S, const bf16* __restrict__ qbuf,
+                                                                          const bf16* __restrict__ pool, bf16* __restrict__ out) {
+    constexpr int LD = DK + 8, LDW = KT + 8;
+    extern __shared__ __align__(16) unsigned char sf_smem[];
+    const AttnArgs& A = S.a;
+    const int H = A.H, G = A.G, d = A.d;
+    bf16* Ks = reinterpret_cast<bf16*>(sf_smem);              // [G][KT][LD]
+    bf16* Vs = Ks + (size_t)G * KT * LD;                      // [G][KT][LD]
+    float* Ws = reinterpret_cast<float*>(Vs + (size_t)G * KT * LD);      // [H][16][LDW]
+    float* tk = Ws + (size_t)H * 16 * LDW;                    // [H][H]
+    const int s = blockIdx.y;
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    if (n <= kShortSeq || tile * 16 >= n) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3, nw = blockDim.x >> 5;
+    const int pos0 = A.tok_pos[t0];
+    const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
+    const int row_a = tile * 16 + gq, row_b = row_a + 8;
+    const bool in_a = row_a < n, in_b = row_b < n;
+    const int i_a = pos0 + row_a, i_b = pos0 + row_b;
+    const int lo_a = sigmoid_first_key(S, i_a), lo_b = sigmoid_first_key(S, i_b);
+    const int last_pos = pos0 + min(n, tile * 16 + 16) - 1;
+    const int j_start = sigmoid_first_key(S, pos0 + tile * 16) / KT * KT;
+    for (int i = threadIdx.x; i < H * H; i += blockDim.x) tk[i] = S.talk[i];
+    float o[HPW][DK / 8][4];
+#pragma unroll
+    for (int u = 0; u < HPW; ++u)
+#pragma unroll
+        for (int nt = 0; nt < DK / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[u][nt][e] = 0.0f;
+    for (int j0 = j_start; j0 <= last_pos; j0 += KT) {
+        __syncthreads();                       // every warp is done with the previous tile
+        for (int idx = threadIdx.x; idx < G * KT * (DK / 8); idx += blockDim.x) {
+            const int c8 = (idx % (DK / 8)) * 8, r = (idx / (DK / 8)) % KT, gk = idx / ((DK / 8) * KT);
+            const int j = j0 + r;
+            uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+            if (j <= last_pos && c8 < d) {
+                const bf16* base = pool + (size_t)bt[j / A.page_size] * A.page_elems;
+                const size_t in_pg = (size_t)gk * A.page_size + j % A.page_size;
+                kv = *reinterpret_cast<const uint4*>(base + A.k_off + in_pg * A.k_ld + c8);
+                vv = *reinterpret_cast<const uint4*>(base + A.v_off + in_pg * A.v_ld + c8);
+            }
+            *reinterpret_cast<uint4*>(Ks + ((size_t)gk * KT + r) * LD + c8) = kv;
+            *reinterpret_cast<uint4*>(Vs + ((size_t)gk * KT + r) * LD + c8) = vv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < HPW; ++u) {
+            const int g = warp + u * nw;
+            if (g >= H) break;
+            const bf16* Kt = Ks + (size_t)(g / (H / G)) * KT * LD;
+            const float hb = S.head_bias[g];
+            float sc[KT / 8][4];
+#pragma unroll
+            for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nt][e] = 0.0f;
+            const bf16* qa = qbuf + ((size_t)(t0 + row_a) * H + g) * d + tq * 2;
+            const bf16* qb = qbuf + ((size_t)(t0 + row_b) * H + g) * d + tq * 2;
+#pragma unroll
+            for (int kk = 0; kk < DK / 16; ++kk) {
+                const int c = kk * 16 + tq * 2;
+                const uint32_t a0 = (in_a && c < d) ? *reinterpret_cast<const uint32_t*>(qa + kk * 16) : 0u;
+                const uint32_t a1 = (in_b && c < d) ? *reinterpret_cast<const uint32_t*>(qb + kk * 16) : 0u;
+                const uint32_t a2 = (in_a && c + 8 < d) ? *reinterpret_cast<const uint32_t*>(qa + kk * 16 + 8) : 0u;
+                const uint32_t a3 = (in_b && c + 8 < d) ? *reinterpret_cast<const uint32_t*>(qb + kk * 16 + 8) : 0u;
+#pragma unroll
+                for (int nt = 0; nt < KT / 8; ++nt) {
+                    const bf16* p = Kt + (nt * 8 + gq) * LD + kk * 16 + tq * 2;
+                    mma_bf16_16816(sc[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(p), *reinterpret_cast<const uint32_t*>(p + 8));
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < KT / 8; ++nt) {
+                float wv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + nt * 8 + tq * 2 + (e & 1);
+                    const bool see = e < 2 ? (in_a && j <= i_a && j >= lo_a) : (in_b && j <= i_b && j >= lo_b);
+                    wv[e] = see ? __fdividef(1.0f, 1.0f + __expf(-fmaf(sc[nt][e], A.scale, hb))) : 0.0f;
+                }
+                float* wp = Ws + ((size_t)g * 16 + gq) * LDW + nt * 8 + tq * 2;
+                *reinterpret_cast<float2*>(wp) = make_float2(wv[0], wv[1]);
+                *reinterpret_cast<float2*>(wp + 8 * LDW) = make_float2(wv[2], wv[3]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < HPW; ++u) {
+            const int h = warp + u * nw;
+            if (h >= H) break;
+            const bf16* Vt = Vs + (size_t)(h / (H / G)) * KT * LD;
+            const float* th = tk + h * H;
+#pragma unroll
+            for (int k2 = 0; k2 < KT / 16; ++k2) {
+                float m[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) m[e] = 0.0f;
+                const float* wp = Ws + (size_t)gq * LDW + k2 * 16 + tq * 2;
+                for (int g = 0; g < H; ++g) {
+                    const float tg = th[g];
+                    const float* p = wp + (size_t)g * 16 * LDW;
+                    const float2 x0 = *reinterpret_cast<const float2*>(p), x1 = *reinterpret_cast<const float2*>(p + 8 * LDW);
+                    const float2 x2 = *reinterpret_cast<const float2*>(p + 8), x3 = *reinterpret_cast<const float2*>(p + 8 * LDW + 8);
+                    m[0] = fmaf(tg, x0.x, m[0]); m[1] = fmaf(tg, x0.y, m[1]); m[2] = fmaf(tg, x1.x, m[2]); m[3] = fmaf(tg, x1.y, m[3]);
+                    m[4] = fmaf(tg, x2.x, m[4]); m[5] = fmaf(tg, x2.y, m[5]); m[6] = fmaf(tg, x3.x, m[6]); m[7] = fmaf(tg, x3.y, m[7]);
+                }
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float h0 = bf16_round(m[2 * e]), h1 = bf16_round(m[2 * e + 1]);
+                    hi[e] = pack_bf16(h0, h1);
+                    lo[e] = pack_bf16(m[2 * e] - h0, m[2 * e + 1] - h1);
+                }
+#pragma unroll
+                for (int nt = 0; nt < DK / 8; ++nt) {
+                    uint32_t b0, b1;
+                    ldmatrix_x2_trans(b0, b1, Vt + (k2 * 16 + (lane & 15)) * LD + nt * 8);
+                    mma_bf16_16816(o[u][nt], hi[0], hi[1], hi[2], hi[3], b0, b1);
+                    mma_bf16_16816(o[u][nt], lo[0], lo[1], lo[2], lo[3], b0, b1);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        const int h = warp + u * nw;
+        if (h >= H) break;
+#pragma unroll
+        for (int nt = 0; nt < DK / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = e < 2 ? row_a : row_b, c = nt * 8 + tq * 2 + (e & 1);
+                if (row < n && c < A.dv) {
+                    const size_t t = t0 + row;
+                    out[t * A.out_ld + h * A.dv + c] = __float2bfloat16_rn(o[u][nt][e] * attn_gate(A, t, h, c));
+                }
+            }
     }
 }
 

@@ -111,3 +111,15 @@ def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
 
 
 TOL = {torch.float32: 3e-4, torch.bfloat16: 8e-2}
+
+
+def close_enough(got: torch.Tensor, want: torch.Tensor, dtype, flips: int = 0, tol=None) -> bool:
+    """fp32: every row within the tolerance.  bf16: a router's close call may go the other way, and the recurrences and the
+    layers above carry that row's difference on to later rows (at a width of 64 and nine layer runs rounding alone reaches
+    half the tolerance) -- the bulk of the rows is held to the tolerance (the median to three quarters of it, three rows in
+    four to all of it), not every row."""
+    errs = row_errs(got, want)
+    tol = tol or TOL[dtype]
+    if dtype == torch.float32:
+        return int((errs > tol).sum()) <= flips
+    return float(errs.median()) < 0.75 * tol and float((errs > tol).double().mean()) <= 0.25

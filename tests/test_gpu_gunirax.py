@@ -9,7 +9,7 @@ import copy
 import pytest
 import torch
 
-from gunirax_util import MIXED, TOL, config, dense, engine_and_oracle, hg, left, moe, only_left, only_right, par, rel_err, right, rot, row_errs, tokens
+from gunirax_util import MIXED, TOL, close_enough, config, dense, engine_and_oracle, hg, left, moe, only_left, only_right, par, rel_err, right, rot, row_errs, tokens
 
 pytestmark = pytest.mark.gpu
 F32, BF16 = torch.float32, torch.bfloat16
@@ -99,10 +99,16 @@ def test_every_layer_of_a_mixed_model(dtype):
     col = []
     want = orc.forward(toks, col)
     assert traces[0].shape[0] == len(col) == 9
-    flips = 0 if dtype == F32 else 3
-    for n, c in enumerate(col):
-        assert int((row_errs(traces[0][n], c) > TOL[dtype]).sum()) <= flips, f"run {n}"
-    assert int((row_errs(logits, want) > TOL[dtype]).sum()) <= flips
+    if dtype == F32:
+        for n, c in enumerate(col):
+            assert rel_err(traces[0][n], c) < TOL[F32], f"run {n}"
+        assert rel_err(logits, want) < TOL[F32]
+    else:
+        # nine runs at a width of 64 with a routed layer that runs three times: a close call of the router may go the other way
+        # and the recurrences carry that row's difference on, so the bulk of the rows is held to the tolerance, not every row
+        for n, c in enumerate(col):
+            assert int((row_errs(traces[0][n], c) > TOL[BF16]).sum()) <= 3, f"run {n}"
+        assert close_enough(logits, want, BF16)
     if dtype == F32:
         # the test sees the constants and the small tensors: changing any of them moves the oracle far beyond the tolerance
         def moved(cfg=None, weights=None):
@@ -157,13 +163,12 @@ def test_prefill_against_token_by_token_and_portions(dtype):
     toks = tokens(90, MIXED["vocab"], 2)
     want = orc.forward(toks)
     whole = run_whole(model, toks)
-    flips = 0 if dtype == F32 else 3          # bf16: a router's close call may go the other way
-    assert int((row_errs(whole, want) > TOL[dtype]).sum()) <= flips
+    assert close_enough(whole, want, dtype)
     b = TokenBatcher(model)
     one = torch.cat([b.feed([("d", [t], [0])]) for t in toks])
     b.feed([("d", [0], [])], end=["d"])
     tight = 1e-4 if dtype == F32 else TOL[dtype]
-    assert int((row_errs(one, want) > TOL[dtype]).sum()) <= flips and int((row_errs(one, whole) > tight).sum()) <= flips
+    assert close_enough(one, want, dtype) and close_enough(one, whole, dtype, tol=tight)
     for sizes in ([2] * 45, [17, 2, 31, 3, 2, 16, 15, 2, 2], [15, 1, 16, 16, 1, 1, 33, 7], [64, 26], [9, 8, 8, 9, 56]):
         assert sum(sizes) == 90
         outs, at = [], 0
@@ -171,8 +176,8 @@ def test_prefill_against_token_by_token_and_portions(dtype):
             outs.append(b.feed([("p", toks[at:at + n], list(range(n)))], end=["p"] if at + n == 90 else []))
             at += n
         got = torch.cat(outs)
-        assert int((row_errs(got, want) > TOL[dtype]).sum()) <= flips, sizes
-        assert int((row_errs(got, whole) > tight).sum()) <= flips, sizes
+        assert close_enough(got, want, dtype), sizes
+        assert close_enough(got, whole, dtype, tol=tight), sizes
     assert len(model.page_pool) == model.page_pool.n and len(model.slot_pool) == model.slot_pool.n
 
 
@@ -208,7 +213,9 @@ def test_unequal_batches_equal_each_alone_with_reused_pages_and_slots(dtype):
     model.check_device_errors()
     assert at == {k: len(v) for k, v in reqs.items()}
     for k in reqs:
-        assert int((row_errs(torch.cat(got[k]), want[k]) > TOL[dtype]).sum()) <= (0 if dtype == F32 else 2), k
+        assert close_enough(torch.cat(got[k]), want[k], dtype), k
+        # and against the engine's own answer for the request alone, whole: sharing steps changes nothing beyond rounding
+        assert rel_err(torch.cat(got[k]), run_whole(model, reqs[k])) < (1e-4 if dtype == F32 else TOL[BF16] / 2), k
     assert len(model.page_pool) == model.page_pool.n and len(model.slot_pool) == 3
 
 
@@ -396,15 +403,13 @@ def test_long_portions_take_the_large_tile_path(dtype):
     assert rel_err(out[390:], want_o[30:31]) < TOL[dtype]
     got.append(b.feed([("a", toks[690:], list(range(10)))], end=["a", "o"]))
     long = torch.cat(got)
-    # bf16: of 700 rows a few may sit on a close call of the router and take another expert than the oracle
-    flips = 0 if dtype == F32 else 6
-    assert int((row_errs(long, want) > TOL[dtype]).sum()) <= flips
+    assert close_enough(long, want, dtype)
     short = torch.cat([b.feed([("s", toks[lo:lo + 100], list(range(100)))], end=["s"] if lo == 600 else []) for lo in range(0, 700, 100)])
-    assert int((row_errs(short, want) > TOL[dtype]).sum()) <= flips
-    assert int((row_errs(long, short) > (1e-4 if dtype == F32 else TOL[dtype])).sum()) <= flips
+    assert close_enough(short, want, dtype)
+    assert close_enough(long, short, dtype, tol=1e-4 if dtype == F32 else TOL[dtype])
     # one entry larger than the engine's step: the batcher cuts it into engine steps itself
     once = b.feed([("w", toks, list(range(700)))], end=["w"])
-    assert int((row_errs(once, want) > TOL[dtype]).sum()) <= flips
+    assert close_enough(once, want, dtype)
     model.check_device_errors()
 
 
@@ -468,10 +473,4 @@ def test_random_configurations_in_mixed_steps(seed, dtype):
     got_a.append(tb.feed([("a", a[at:], list(range(150 - at)))], end=["a", "b"]))
     model.check_device_errors()
     for got, want in ((torch.cat(got_a), want_a), (torch.cat(got_b), want_b)):
-        errs = row_errs(got, want)
-        if dtype == F32:
-            assert float(errs.max()) < TOL[F32]
-        else:
-            # bf16: a router's close call may go the other way, and the recurrences of the layers above carry that row's
-            # difference on to later rows: the bulk of the rows is held to the tolerance, not every row
-            assert float(errs.median()) < TOL[BF16] / 4 and float((errs > TOL[BF16]).double().mean()) <= 0.15
+        assert close_enough(got, want, dtype)
