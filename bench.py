@@ -113,8 +113,8 @@ def parse_args():
     ap.add_argument("--cpu-frames", type=int, default=0, help="frames of the CPU sample (0 = %d)" % CPU_SAMPLE_FRAMES)
     ap.add_argument("--lm", action="store_true", help="instead of the default workload: prefill / decode tokens/s of the hybrid "
                     "language-model engine at a few layer sizes beside the DualAR slow transformer (smoltts_b200/lm_bench.py)")
-    ap.add_argument("--lm-design", choices=["pamasun", "maferax", "sunutar"], default="pamasun", help="--lm: pamasun (beside the DualAR slow transformer) "
-                    "or maferax / sunutar (beside Pamasun at equal width, depth and head count)")
+    ap.add_argument("--lm-design", choices=["pamasun", "maferax", "sunutar", "gunirax"], default="pamasun", help="--lm: pamasun (beside the DualAR slow transformer) "
+                    "or maferax / sunutar (beside Pamasun at equal width, depth and head count) or gunirax (beside Sunutar)")
     ap.add_argument("--lm-sizes", default="", help="--lm: comma list of sizes (default: all of lm_bench.SIZES)")
     ap.add_argument("--lm-prompt", type=int, default=2048, help="--lm: prompt tokens / cached context")
     ap.add_argument("--opt", action="append", default=[], help="engine option name=value (smol_set_option), repeatable")

@@ -1,6 +1,7 @@
 """Prefill and decode throughput of the hybrid language-model engine at layer sizes that resemble a real model's:
 the Pamasun design beside the DualAR slow transformer (the package's closest model: attention + gated MLP layers), and the
-Maferax and Sunutar designs beside Pamasun at equal width, depth and head count (``--lm-design maferax`` / ``sunutar``).
+Maferax and Sunutar designs beside Pamasun at equal width, depth and head count (``--lm-design maferax`` / ``sunutar``),
+and the Gunirax design beside Sunutar (``--lm-design gunirax``).
 
 ``python bench.py --lm`` prints one JSON line: for every size, tokens/s of a whole-prompt prefill and of single-token
 decode steps against a filled cache, each with its distance from the roofline (matrix-product + attention flops over the
@@ -249,6 +250,123 @@ def bench_sunutar(name: str, prompt: int, batch: int, decode_steps: int, warmup:
             "gpu_launches": int(launches)}
 
 
+GUNIRAX_SIZES = {
+    # parallel layers: sigmoid attention heads x dim over kv_heads in chunks of `chunk` beside lightning attention r_heads x (r_dim keys,
+    # r_vdim values); every fifth layer is HGRN2 with the lightning attention's sizes; feed-forward: dense gated units (ff), on every
+    # second layer routed squared-relu experts (top of experts, size eff, 4 groups of which 2 are kept) and a shared expert of size eff
+    "w768": dict(width=768, layers=10, heads=12, kv_heads=4, dim=64, chunk=1024, r_heads=12, r_dim=128, r_vdim=64, ff=3072, experts=16, top=2,
+                 eff=1024, vocab=2368),
+    "w768dense": dict(width=768, layers=10, heads=12, kv_heads=4, dim=64, chunk=1024, r_heads=12, r_dim=128, r_vdim=64, ff=3072, experts=0, top=0,
+                      eff=0, vocab=2368),
+    "w1536": dict(width=1536, layers=12, heads=12, kv_heads=4, dim=128, chunk=1024, r_heads=24, r_dim=128, r_vdim=64, ff=4096, experts=32, top=4,
+                  eff=1024, vocab=8192),
+}
+
+
+def gunirax_config(width, layers, heads, kv_heads, dim, chunk, r_heads, r_dim, r_vdim, ff, experts, top, eff, vocab) -> dict:
+    ls = []
+    for i in range(layers):
+        mlp = ({"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}, "scale": 1.5},
+                "shared": {"ff": eff}} if experts and i % 2 else {"kind": "dense", "ff": ff})
+        if i % 5 == 4:
+            ls.append({"type": "hgrn2", "mixer": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim}, "mlp": mlp})
+            continue
+        ls.append({"type": "parallel", "mlp": mlp,
+                   "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": chunk}, "scale": dim ** -0.5,
+                                      "rot": {"base": 10000.0, "dims": dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}},
+                             "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim,
+                                       "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(r_heads - 1, 1)) for h in range(r_heads)]}}})
+    return {"architecture": "Gunirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": ls}
+
+
+def gunirax_state_dict(cfg, seed: int = 0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for k, s in cfg.tensor_shapes().items():
+        if k.endswith(".talk"):
+            sd[k] = (torch.eye(s[0]) * 0.7 + torch.randn(*s, generator=g) * 0.1).bfloat16()
+        elif len(s) == 2:
+            sd[k] = (torch.randn(*s, generator=g) * (s[1] ** -0.5)).bfloat16()
+        elif k.endswith(".alpha"):
+            sd[k] = torch.tensor(0.5).bfloat16()
+        elif k.endswith(".lower"):
+            sd[k] = (torch.rand(s, generator=g) * 0.9).bfloat16()
+        elif k.endswith((".b", ".pb", "correction")):
+            sd[k] = (torch.randn(*s, generator=g) * 0.05).bfloat16()
+        else:
+            sd[k] = torch.ones(s).bfloat16()
+    sd["embed"] = torch.randn(*sd["embed"].shape, generator=g).bfloat16()
+    return sd
+
+
+def bench_gunirax(name: str, prompt: int, batch: int, decode_steps: int, warmup: int, steps: int, peaks) -> dict:
+    """Like bench_sunutar.  Prefill flops: matrix products of the weights one token touches, sigmoid attention over the keys of
+    the query's chunk (2 dim for the score, 2 heads for mixing the heads' weights, 2 dim for the values, per visible key and
+    head) and the recurrences (6 dim vdim per head and token); decode bytes: the weights one step touches (every expert only
+    if the batch's choices can cover them all), the keys and values of the current chunk, and the states (read and written)."""
+    from .lm import GuniraxLM
+    from .lm_config import GuniraxConfig
+
+    hbm, tflops, _ = peaks
+    spec = GUNIRAX_SIZES[name]
+    cfg = GuniraxConfig.from_dict(gunirax_config(**spec))
+    model = GuniraxLM(cfg, dtype=torch.bfloat16, max_tokens=batch * (prompt + 64 + decode_steps), max_seqs=batch, page_size=64,
+                      max_step_tokens=2048, max_want=batch)
+    model.load_state_dict(gunirax_state_dict(cfg, 0))
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg.vocab, (batch, prompt + decode_steps), generator=g).tolist()
+    n_par = sum(1 for L in cfg.layers if L.kind == "parallel")
+    n_rec = len(cfg.layers)                                    # every layer carries one recurrence of the same size
+    H, G, d, C = spec["heads"], spec["kv_heads"], spec["dim"], spec["chunk"]
+    rH, rd, rdv = spec["r_heads"], spec["r_dim"], spec["r_vdim"]
+    mm_flops = cfg.matmul_flops_per_token() - 2 * cfg.vocab * cfg.width
+
+    def prefill():
+        seq = model.open_sequence()
+        for lo in range(0, prompt, model.max_step_tokens):
+            part = toks[0][lo:min(prompt, lo + model.max_step_tokens)]
+            model.forward([(seq, part, [len(part) - 1] if lo + len(part) == prompt else [])])
+        model.close_sequence(seq)
+
+    l0 = model.launch_count
+    ms_p = _timed(prefill, warmup, steps)
+    launches = model.launch_count - l0
+    visible = sum(i % C + 1 for i in range(prompt))
+    flops_p = prompt * mm_flops + n_par * H * (4 * d + 2 * H) * visible + n_rec * 6 * rH * rd * rdv * prompt
+    seqs = [model.open_sequence() for _ in range(batch)]
+    for b, s in enumerate(seqs):
+        for lo in range(0, prompt, model.max_step_tokens):
+            model.forward([(s, toks[b][lo:min(prompt, lo + model.max_step_tokens)], [])])
+
+    def decode():
+        for i in range(decode_steps):
+            model.forward([(s, [toks[b][prompt + i]], [0]) for b, s in enumerate(seqs)])
+        for s in seqs:
+            s.length = prompt
+
+    l0 = model.launch_count
+    ms_d = _timed(decode, 2, steps) / decode_steps
+    launches += model.launch_count - l0
+    ctx = sum((prompt + i) % C + 1 for i in range(decode_steps)) / decode_steps
+    all_w, act_w = cfg.weight_elements(), cfg.weight_elements(active_only=True)
+    touched = act_w
+    if spec["experts"]:
+        per_expert = (all_w - act_w) / max(spec["experts"] - spec["top"], 1)
+        touched = all_w - per_expert * max(spec["experts"] - min(batch * spec["top"], spec["experts"]), 0)
+    kv_bytes = n_par * G * 2 * d * 2 * ctx * batch
+    st_bytes = n_rec * 2 * rH * rd * rdv * 4 * batch
+    bytes_d = 2 * touched + kv_bytes + st_bytes
+    model.check_device_errors()
+    for s in seqs:
+        model.close_sequence(s)
+    return {"model": f"Gunirax {name}", "spec": spec, "parameters_m": round(all_w / 1e6, 1), "active_parameters_m": round(act_w / 1e6, 1),
+            "prefill": {"prompt": prompt, "tokens_per_s": prompt / ms_p * 1e3, "ms": ms_p, "tflops": flops_p / ms_p / 1e9,
+                        "of_peak": flops_p / ms_p / 1e9 / tflops},
+            "decode": {"batch": batch, "context": prompt, "tokens_per_s": batch / ms_d * 1e3, "ms_per_step": ms_d,
+                       "gbs": bytes_d / ms_d / 1e6, "of_peak": bytes_d / ms_d / 1e6 / hbm},
+            "gpu_launches": int(launches)}
+
+
 def pamasun_config(width, layers, heads, kv_heads, dim, ff, vocab, pattern) -> dict:
     ls = []
     for i in range(layers):
@@ -420,7 +538,17 @@ def run(args, root: str) -> None:
     peaks = _peaks(root)
     t0 = time.time()
     entries: List[dict] = []
-    if getattr(args, "lm_design", "pamasun") == "sunutar":
+    if getattr(args, "lm_design", "pamasun") == "gunirax":
+        # Gunirax beside Sunutar (the engine's closest design: every mixer a pair of an attention and a recurrence on the same input,
+        # dense and routed feed-forwards) at equal width, depth, heads and state sizes
+        names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768dense", "w1536"])]
+        for n in names:
+            for batch in (1, 4):
+                entries.append(bench_gunirax(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+        for n in names:
+            for batch in (1, 4):
+                entries.append(bench_sunutar(n, args.lm_prompt, batch, 16, args.warmup, args.steps, peaks))
+    elif getattr(args, "lm_design", "pamasun") == "sunutar":
         # Sunutar beside Pamasun (the engine's closest design: the same block, attention and a recurrence) at equal width, depth and heads
         names = [n for n in (args.lm_sizes.split(",") if args.lm_sizes else ["w768", "w768dense", "w1536"])]
         for n in names:
