@@ -1519,7 +1519,8 @@ struct SmolLm {
     // post-norm block: every layer result of the step; latent attention: query latent (T), full query (fp32 and T), query in
     // latent space (fp32), rotation frequencies; routed feed-forward: choices, sorted order, tile table, per-pair buffers
     size_t o_hist = 0, o_cq = 0, o_qf = 0, o_freq = 0;
-    size_t o_x0 = 0, o_mix2 = 0, o_y2 = 0;    // pre-norm block: the embedding output; mixers with their own output projections: the second result
+    size_t o_x0 = 0, o_mix2 = 0, o_y2 = 0, o_spart = 0;
+    int max_sig_cols = 0;                     // sigmoid attention: widest heads * vdim (partial sums of the tiled kernel's key ranges)    // pre-norm block: the embedding output; mixers with their own output projections: the second result
     size_t o_rlogits = 0, o_rdone = 0, o_ap = 0, o_sel_id = 0, o_sel_w = 0, o_perm = 0, o_slot_of = 0, o_seg = 0, o_tile_g = 0, o_tile_r = 0, o_ntiles = 0, o_zp = 0, o_actp = 0, o_yp = 0;
     int max_routed = 0, max_cq = 0, max_qf = 0, max_top = 0, max_experts = 0, max_pair_ff = 0;
     std::vector<float> freq_table;
@@ -1666,6 +1667,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             m->page_elems = r.v_off + (size_t)L.kv_heads * cfg->page_size * L.vdim;
             r.freq_off = m->freq_table.size();
             push_frequencies(m->freq_table, L, true);
+            m->max_sig_cols = std::max(m->max_sig_cols, L.heads * L.vdim);
             m->max_q = std::max(m->max_q, L.heads * L.dim);
             m->max_heads = std::max(m->max_heads, L.heads);
             m->max_vdim = std::max(m->max_vdim, L.vdim);
@@ -1784,6 +1786,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
     }
     if (!m->freq_table.empty()) m->o_freq = carve(m->freq_table.size() * 4 + 4);
     if (m->any_restart) m->o_x0 = carve(T * D * 4);
+    if (m->max_sig_cols > 0 && cfg->dtype == SMOL_LM_BF16) m->o_spart = carve((size_t)kSigmoidRanges * T * m->max_sig_cols * 4);
     if (m->any_own_proj) {
         m->o_mix2 = carve(T * (size_t)std::max(m->max_mix, 1) * E);
         m->o_y2 = carve(T * D * 4);
@@ -2105,11 +2108,24 @@ static bool launch_sigmoid_flash_sized(const SigmoidArgs& S, dim3 grid, int thre
     }
     return false;
 }
-static bool launch_sigmoid_flash(SmolLm* m, const SmolLmStep* s, const SigmoidArgs& S, int max_n, const bf16* qbuf, const bf16* pool, bf16* out,
+static bool launch_sigmoid_flash(SmolLm* m, const SmolLmStep* s, SigmoidArgs& S, int max_n, const bf16* qbuf, const bf16* pool, bf16* out,
                                  bool is_bf16, cudaStream_t st) {
     const AttnArgs& A = S.a;
     if (!is_bf16 || A.d % 8 != 0 || A.d > 128 || A.k_off % 8 != 0 || A.v_off % 8 != 0) return false;
-    const dim3 grid((max_n + 15) / 16, s->n_seqs);
+    // Key ranges: a quarter of the positions a row tile can see (at least 256, whole 64-key tiles), more only where that
+    // would cut a tile into more than kSigmoidRanges ranges.  The ranges depend on the mask and the pool's size alone.
+    const int span = S.chunk > 0 ? std::min(S.chunk + 15, m->cfg.max_context) : m->cfg.max_context;
+    auto ranges_of = [&](int len) { return S.chunk > 0 ? (span + len - 1) / len + 1 : (span + len - 1) / len; };
+    int len = std::max(256, ((span + 3) / 4 + 63) / 64 * 64);
+    while (ranges_of(len) > kSigmoidRanges) len += 64;
+    S.range_len = len;
+    S.n_ranges = ranges_of(len);
+    if (span <= 512) {                       // few keys per row: one range, the result written directly
+        S.range_len = 1 << 30;
+        S.n_ranges = 1;
+    }
+    S.partial = reinterpret_cast<float*>(m->ws + m->o_spart);
+    const dim3 grid((max_n + 15) / 16, s->n_seqs, S.n_ranges);
     bool done;
     if (A.H <= 16) {
         const int threads = A.H * 32;
@@ -2122,6 +2138,10 @@ static bool launch_sigmoid_flash(SmolLm* m, const SmolLmStep* s, const SigmoidAr
         if (A.d <= 32) done = launch_sigmoid_flash_sized<32, 2>(S, grid, threads, qbuf, pool, out, st);
         else if (A.d <= 64) done = launch_sigmoid_flash_sized<64, 2>(S, grid, threads, qbuf, pool, out, st);
         else done = false;
+    }
+    if (done && S.n_ranges > 1) {
+        sigmoid_merge_kernel<<<A.n_tokens, 128, 0, st>>>(S, out);
+        m->launches += 1;
     }
     if (done) m->launches += 1;
     return done;

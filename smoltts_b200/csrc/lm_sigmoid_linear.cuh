@@ -140,7 +140,18 @@ struct SigmoidArgs {
     const float* freq;             // [rot_pairs]
     const float *head_bias, *talk; // [H], [H][H]
     int skip_long;                 // 1: the warp-per-head kernel leaves sequences of more than kShortSeq tokens to the tiled kernel
+    // tiled kernel: the keys are cut into absolute ranges of range_len positions (a multiple of its key tile), one block per
+    // (row tile, sequence, range); with more than one range the blocks leave fp32 partial sums in `partial`
+    // [n_ranges][tokens][H * dv] and sigmoid_merge_kernel adds them in range order (the weights are not normalised, so
+    // partial sums simply add)
+    int range_len, n_ranges;
+    float* partial;
 };
+// ranges a row tile touches: from the range of its first row's first key to the range of its last row's position
+__device__ __forceinline__ int sigmoid_tile_ranges(const SigmoidArgs& S, int first_pos, int last_pos, int& r0) {
+    r0 = (S.chunk > 0 ? first_pos / S.chunk * S.chunk : 0) / S.range_len;
+    return last_pos / S.range_len - r0 + 1;
+}
 __device__ __forceinline__ int sigmoid_first_key(const SigmoidArgs& S, int pos) { return S.chunk > 0 ? pos / S.chunk * S.chunk : 0; }
 
 // One warp per (token, slot): slots 0..H-1 prepare a query head (bias, rotation, division by the root mean square) into
@@ -204,6 +215,7 @@ __global__ void sigmoid_prep_kernel(const SigmoidArgs S, T* __restrict__ qbuf, T
 // mixing matrix and adds the weighted values of its key/value head.  Keys are walked from the first key of the
 // query's chunk in absolute rounds, so a row's sum does not depend on how the step was cut.
 constexpr int kSigmoidMaxHeads = 32;
+constexpr int kSigmoidRanges = 6;             // most key ranges a row tile of the tiled kernel is cut into
 
 template <class T, int MAXV>
 __global__ void __launch_bounds__(kSigmoidMaxHeads * 32) sigmoid_attn_kernel(const SigmoidArgs S, const T* __restrict__ qbuf,
@@ -272,7 +284,8 @@ __global__ void __launch_bounds__(kSigmoidMaxHeads * 32) sigmoid_attn_kernel(con
 //      kept) and adds weights x values on the tensor cores.
 // Masked keys weigh exactly zero, and tiles are absolute positions, so a row's sum does not depend on how the step was cut.
 // The sigmoid uses the hardware exponential and division (relative error about 2^-21; this form serves bf16 only).
-// Needs d % 8 == 0 and 16-byte aligned cached rows.
+// Needs d % 8 == 0 and 16-byte aligned cached rows.  blockIdx.z is the key range (see SigmoidArgs): a chunk's last rows see
+// many more keys than its first ones, and ranges spread them over the SMs.
 template <int DK, int HPW, int KT>
 __global__ void __launch_bounds__(HPW == 1 ? 512 : 256) sigmoid_flash_kernel(const SigmoidArgs S, const bf16* __restrict__ qbuf,
                                                                           const bf16* __restrict__ pool, bf16* __restrict__ out) {
@@ -296,8 +309,28 @@ __global__ void __launch_bounds__(HPW == 1 ? 512 : 256) sigmoid_flash_kernel(con
     const int i_a = pos0 + row_a, i_b = pos0 + row_b;
     const int lo_a = sigmoid_first_key(S, i_a), lo_b = sigmoid_first_key(S, i_b);
     const int last_pos = pos0 + min(n, tile * 16 + 16) - 1;
-    const int j_start = sigmoid_first_key(S, pos0 + tile * 16) / KT * KT;
+    int r0;
+    const int n_ranges = sigmoid_tile_ranges(S, pos0 + tile * 16, last_pos, r0);
+    if ((int)blockIdx.z >= n_ranges) return;
+    const int j_start = max(sigmoid_first_key(S, pos0 + tile * 16) / KT * KT, (r0 + (int)blockIdx.z) * S.range_len);
+    const int j_end = min(last_pos, (r0 + (int)blockIdx.z + 1) * S.range_len - 1);
     for (int i = threadIdx.x; i < H * H; i += blockDim.x) tk[i] = S.talk[i];
+    // the queries of this warp's heads stay in registers as A fragments
+    uint32_t qf[HPW][DK / 16][4];
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        const int g = min(warp + u * nw, H - 1);
+        const bf16* qa = qbuf + ((size_t)(t0 + row_a) * H + g) * d + tq * 2;
+        const bf16* qb = qbuf + ((size_t)(t0 + row_b) * H + g) * d + tq * 2;
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk) {
+            const int c = kk * 16 + tq * 2;
+            qf[u][kk][0] = (in_a && c < d) ? *reinterpret_cast<const uint32_t*>(qa + kk * 16) : 0u;
+            qf[u][kk][1] = (in_b && c < d) ? *reinterpret_cast<const uint32_t*>(qb + kk * 16) : 0u;
+            qf[u][kk][2] = (in_a && c + 8 < d) ? *reinterpret_cast<const uint32_t*>(qa + kk * 16 + 8) : 0u;
+            qf[u][kk][3] = (in_b && c + 8 < d) ? *reinterpret_cast<const uint32_t*>(qb + kk * 16 + 8) : 0u;
+        }
+    }
     float o[HPW][DK / 8][4];
 #pragma unroll
     for (int u = 0; u < HPW; ++u)
@@ -305,7 +338,7 @@ __global__ void __launch_bounds__(HPW == 1 ? 512 : 256) sigmoid_flash_kernel(con
         for (int nt = 0; nt < DK / 8; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) o[u][nt][e] = 0.0f;
-    for (int j0 = j_start; j0 <= last_pos; j0 += KT) {
+    for (int j0 = j_start; j0 <= j_end; j0 += KT) {
         __syncthreads();                       // every warp is done with the previous tile
         for (int idx = threadIdx.x; idx < G * KT * (DK / 8); idx += blockDim.x) {
             const int c8 = (idx % (DK / 8)) * 8, r = (idx / (DK / 8)) % KT, gk = idx / ((DK / 8) * KT);
@@ -332,21 +365,14 @@ __global__ void __launch_bounds__(HPW == 1 ? 512 : 256) sigmoid_flash_kernel(con
             for (int nt = 0; nt < KT / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) sc[nt][e] = 0.0f;
-            const bf16* qa = qbuf + ((size_t)(t0 + row_a) * H + g) * d + tq * 2;
-            const bf16* qb = qbuf + ((size_t)(t0 + row_b) * H + g) * d + tq * 2;
 #pragma unroll
-            for (int kk = 0; kk < DK / 16; ++kk) {
-                const int c = kk * 16 + tq * 2;
-                const uint32_t a0 = (in_a && c < d) ? *reinterpret_cast<const uint32_t*>(qa + kk * 16) : 0u;
-                const uint32_t a1 = (in_b && c < d) ? *reinterpret_cast<const uint32_t*>(qb + kk * 16) : 0u;
-                const uint32_t a2 = (in_a && c + 8 < d) ? *reinterpret_cast<const uint32_t*>(qa + kk * 16 + 8) : 0u;
-                const uint32_t a3 = (in_b && c + 8 < d) ? *reinterpret_cast<const uint32_t*>(qb + kk * 16 + 8) : 0u;
+            for (int kk = 0; kk < DK / 16; ++kk)
 #pragma unroll
                 for (int nt = 0; nt < KT / 8; ++nt) {
                     const bf16* p = Kt + (nt * 8 + gq) * LD + kk * 16 + tq * 2;
-                    mma_bf16_16816(sc[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(p), *reinterpret_cast<const uint32_t*>(p + 8));
+                    mma_bf16_16816(sc[nt], qf[u][kk][0], qf[u][kk][1], qf[u][kk][2], qf[u][kk][3], *reinterpret_cast<const uint32_t*>(p),
+                                   *reinterpret_cast<const uint32_t*>(p + 8));
                 }
-            }
 #pragma unroll
             for (int nt = 0; nt < KT / 8; ++nt) {
                 float wv[4];
@@ -410,9 +436,27 @@ __global__ void __launch_bounds__(HPW == 1 ? 512 : 256) sigmoid_flash_kernel(con
                 const int row = e < 2 ? row_a : row_b, c = nt * 8 + tq * 2 + (e & 1);
                 if (row < n && c < A.dv) {
                     const size_t t = t0 + row;
-                    out[t * A.out_ld + h * A.dv + c] = __float2bfloat16_rn(o[u][nt][e] * attn_gate(A, t, h, c));
+                    if (S.n_ranges > 1) S.partial[((size_t)blockIdx.z * A.n_tokens + t) * (H * A.dv) + h * A.dv + c] = o[u][nt][e];
+                    else out[t * A.out_ld + h * A.dv + c] = __float2bfloat16_rn(o[u][nt][e] * attn_gate(A, t, h, c));
                 }
             }
+    }
+}
+
+// Adds a row's partial sums over its key ranges in range order, applies the head's gate and writes bf16.  One block per token.
+__global__ void sigmoid_merge_kernel(const SigmoidArgs S, bf16* __restrict__ out) {
+    const AttnArgs& A = S.a;
+    const int t = blockIdx.x, s = A.tok_seq[t];
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
+    if (n <= kShortSeq) return;
+    const int tile = (t - t0) / 16, pos0 = A.tok_pos[t0];
+    int r0;
+    const int nr = sigmoid_tile_ranges(S, pos0 + tile * 16, pos0 + min(n, tile * 16 + 16) - 1, r0);
+    const int cols = A.H * A.dv;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int z = 0; z < nr; ++z) acc += S.partial[((size_t)z * A.n_tokens + t) * cols + c];
+        out[(size_t)t * A.out_ld + c] = __float2bfloat16_rn(acc * attn_gate(A, t, c / A.dv, c % A.dv));
     }
 }
 

@@ -413,6 +413,27 @@ def test_long_portions_take_the_large_tile_path(dtype):
     model.check_device_errors()
 
 
+@pytest.mark.parametrize("chunk", [600, 1100])
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_large_chunks_split_into_key_ranges(chunk, dtype):
+    """Chunks of many hundred positions: the prompt form of the attention cuts a row's keys into ranges that separate blocks
+    sum; portions that start inside, at and just before a chunk's and a range's edge agree with the oracle and each other."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([par(left(heads=4, kv_heads=2, dim=32, chunk=chunk, scale=0.2, r=rot(16, 1000.0)), right(heads=2, dim=16, vdim=16), dense(64))], vocab=113, width=96)
+    model, orc, _ = engine_and_oracle(cfg, seed=12, dtype=dtype, page_size=64, max_tokens=2048, max_step_tokens=1024)
+    toks = tokens(1300, 113, 33)
+    want = orc.forward(toks)
+    b = TokenBatcher(model)
+    got = torch.cat([b.feed([("a", toks[lo:hi], list(range(hi - lo)))]) for lo, hi in ((0, 700), (700, 1290), (1290, 1300))])
+    b.feed([("a", [1], [])], end=["a"])
+    assert close_enough(got, want, dtype)
+    cuts = [0, 255, 257, chunk - 1, chunk + 16, 1279, 1300]
+    other = torch.cat([b.feed([("c", toks[lo:hi], list(range(hi - lo)))], end=["c"] if hi == 1300 else []) for lo, hi in zip(cuts[:-1], cuts[1:])])
+    assert close_enough(other, want, dtype) and close_enough(other, got, dtype, tol=1e-4 if dtype == F32 else TOL[BF16] / 2)
+    model.check_device_errors()
+
+
 def random_config(seed):
     """A configuration drawn at random: kinds, sizes, counts and constants all differ from layer to layer."""
     import random
