@@ -1851,6 +1851,8 @@ static cudaError_t set_kernel_attributes() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_attn_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_attn_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_split_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSigmoidSmemMax);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(sigmoid_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSigmoidSmemMax);
     if (e == cudaSuccess) e = sigmoid_flash_attributes<32, 1>();
     if (e == cudaSuccess) e = sigmoid_flash_attributes<64, 1>();
     if (e == cudaSuccess) e = sigmoid_flash_attributes<96, 1>();
@@ -2091,7 +2093,6 @@ static void launch_attention(SmolLm* m, const SmolLmStep* s, AttnArgs& A, bool f
 // The tiled sigmoid attention over the sequences that bring more than kShortSeq tokens.  Returns false where this form does
 // not apply (fp32 engine, sizes it is not built for, unaligned cached rows, more shared memory than an SM has): the caller
 // then runs the warp-per-head kernel over every row.
-constexpr int kSigmoidSmemMax = 200 * 1024;
 static size_t sigmoid_flash_smem(int H, int G, int DK, int KT) {
     return (size_t)2 * G * KT * (DK + 8) * sizeof(bf16) + ((size_t)H * 16 * (KT + 8) + (size_t)H * H) * sizeof(float);
 }
@@ -2276,7 +2277,8 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             A.window = 0; A.softcap = A.two_over_cap = 0.0f;
             A.split_len = A.n_splits = A.short_rows = 0; A.part = nullptr;
             A.out_ld = ld; A.out_scale = 1.0f;
-            S.chunk = M.chunk; S.rot_pairs = M.rot_dims / 2; S.head_bias = M.head_bias; S.talk = M.talk; S.skip_long = 0;
+            S.chunk = M.chunk; S.rot_pairs = M.rot_dims / 2; S.head_bias = M.head_bias; S.talk = M.talk; S.only = 0;
+            S.range_len = 1 << 30; S.n_ranges = 1; S.partial = nullptr;
             S.freq = reinterpret_cast<const float*>(m->ws + m->o_freq) + Ri.freq_off;
             const int units = Tn * (M.heads + M.kv_heads);
             sigmoid_prep_kernel<T><<<(units + 3) / 4, 128, 0, st>>>(S, qbuf, pool);
@@ -2286,8 +2288,26 @@ static int step_impl(SmolLm* m, const SmolLmStep* s, cudaStream_t st) {
             // sequences that bring more than a few tokens take the tiled tensor-core form (bf16), the others a warp per head
             const bool tiled = max_n > kShortSeq && launch_sigmoid_flash(m, s, S, max_n, reinterpret_cast<const bf16*>(qbuf), reinterpret_cast<const bf16*>(pool),
                                                                          reinterpret_cast<bf16*>(mix_at), sizeof(T) == 2, st);
-            if (!tiled || min_n <= kShortSeq) {
-                S.skip_long = tiled ? 1 : 0;
+            // sequences of few tokens (decoding): key ranges over separate blocks, merged afterwards
+            const size_t split_smem = sigmoid_split_smem<T>(M.heads, M.kv_heads, M.dim, M.vdim);
+            const bool split = min_n <= kShortSeq && split_smem <= (size_t)kSigmoidSmemMax;
+            if (split) {
+                const int max_pos = s->max_pos > 0 ? std::min(s->max_pos, c.max_context - 1) : c.max_context - 1;
+                A.split_len = m->split_len;
+                A.short_rows = s->n_seqs * kShortSeq;
+                A.part = reinterpret_cast<float*>(m->ws + m->o_part);
+                A.n_splits = std::min(m->max_splits, (max_pos / m->split_len + 4) / 4 * 4);
+                if (M.chunk > 0) A.n_splits = std::min(A.n_splits, ((M.chunk - 1) / m->split_len + 2 + 3) / 4 * 4);      // ranges a chunk can touch
+                const dim3 grid(A.short_rows, A.n_splits);
+                if (M.vdim <= 256) sigmoid_split_kernel<T, 8><<<grid, M.heads * 32, split_smem, st>>>(S, qbuf, pool);
+                else sigmoid_split_kernel<T, 16><<<grid, M.heads * 32, split_smem, st>>>(S, qbuf, pool);
+                sigmoid_short_merge_kernel<T><<<A.short_rows, 128, 0, st>>>(S, mix_at);
+                m->launches += 2;
+            }
+            const bool long_left = max_n > kShortSeq && !tiled, short_left = min_n <= kShortSeq && !split;
+            if (long_left || short_left) {
+                // the warp-per-head form: every row, or only the rows the other two forms left
+                S.only = (long_left && short_left) ? 0 : long_left ? 1 : 2;
                 const size_t smem = ((size_t)M.heads * (M.dim + 32) + (size_t)M.heads * M.heads) * sizeof(float);
                 if (M.vdim <= 256) sigmoid_attn_kernel<T, 8><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);
                 else sigmoid_attn_kernel<T, 16><<<Tn, M.heads * 32, smem, st>>>(S, qbuf, pool, mix_at);

@@ -139,7 +139,7 @@ struct SigmoidArgs {
     int rot_pairs;                 // leading pairs (2i, 2i+1) of a head that are rotated
     const float* freq;             // [rot_pairs]
     const float *head_bias, *talk; // [H], [H][H]
-    int skip_long;                 // 1: the warp-per-head kernel leaves sequences of more than kShortSeq tokens to the tiled kernel
+    int only;                      // which sequences the warp-per-head kernel serves: 0 all, 1 those of more than kShortSeq tokens, 2 the others
     // tiled kernel: the keys are cut into absolute ranges of range_len positions (a multiple of its key tile), one block per
     // (row tile, sequence, range); with more than one range the blocks leave fp32 partial sums in `partial`
     // [n_ranges][tokens][H * dv] and sigmoid_merge_kernel adds them in range order (the weights are not normalised, so
@@ -215,6 +215,7 @@ __global__ void sigmoid_prep_kernel(const SigmoidArgs S, T* __restrict__ qbuf, T
 // mixing matrix and adds the weighted values of its key/value head.  Keys are walked from the first key of the
 // query's chunk in absolute rounds, so a row's sum does not depend on how the step was cut.
 constexpr int kSigmoidMaxHeads = 32;
+constexpr int kSigmoidSmemMax = 200 * 1024;   // shared memory the tiled and the few-token kernels may ask for
 constexpr int kSigmoidRanges = 6;             // most key ranges a row tile of the tiled kernel is cut into
 
 template <class T, int MAXV>
@@ -224,9 +225,9 @@ __global__ void __launch_bounds__(kSigmoidMaxHeads * 32) sigmoid_attn_kernel(con
     const AttnArgs& A = S.a;
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, H = A.H;
     const int t = blockIdx.x;
-    if (S.skip_long) {
+    if (S.only) {
         const int sq = A.tok_seq[t];
-        if (A.seq_start[sq + 1] - A.seq_start[sq] > kShortSeq) return;
+        if ((A.seq_start[sq + 1] - A.seq_start[sq] <= kShortSeq) == (S.only == 1)) return;
     }
     const int g = h / (H / A.G);
     float* qs = sig_smem + h * A.d;
@@ -271,6 +272,103 @@ __global__ void __launch_bounds__(kSigmoidMaxHeads * 32) sigmoid_attn_kernel(con
     for (int e = 0; e < MAXV; ++e) {
         const int c = lane + e * 32;
         if (c < A.dv) out[(size_t)t * A.out_ld + h * A.dv + c] = from_f<T>(o[e] * attn_gate(A, t, h, c));
+    }
+}
+
+// Sigmoid attention for sequences that bring few tokens (decoding, short portions): the keys of a row are cut into fixed
+// absolute ranges of A.split_len positions, one block per (row, range) with a warp per head.  32 keys and values of every
+// key/value head at a time are staged in shared memory by the whole block (rows padded by 16 bytes), so that no global
+// load sits inside the score / mixing / value loops.  The weights are not normalised, so a range's result is a plain
+// partial sum: it goes to A.part [row][range][H * dv] and sigmoid_short_merge_kernel adds the ranges in order and applies
+// the gate.
+template <class T>
+__host__ __device__ inline size_t sigmoid_split_smem(int H, int G, int d, int dv) {
+    const int pad = 16 / (int)sizeof(T);
+    return ((size_t)H * (d + 32) + (size_t)H * H) * sizeof(float) + (size_t)G * 32 * ((d + pad) + (dv + pad)) * sizeof(T);
+}
+
+template <class T, int MAXV>
+__global__ void __launch_bounds__(kSigmoidMaxHeads * 32) sigmoid_split_kernel(const SigmoidArgs S, const T* __restrict__ qbuf, const T* __restrict__ pool) {
+    extern __shared__ __align__(16) unsigned char ss_raw[];
+    constexpr int kPad = 16 / (int)sizeof(T);
+    const AttnArgs& A = S.a;
+    const int H = A.H, G = A.G;
+    const int s = blockIdx.x / kShortSeq, r = blockIdx.x % kShortSeq;
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
+    if (n > kShortSeq || r >= n) return;
+    const int t = t0 + r, pos = A.tok_pos[t];
+    const int j_first = sigmoid_first_key(S, pos);
+    const int range = j_first / A.split_len + blockIdx.y;
+    if (range * A.split_len > pos) return;
+    const int j_lo = max(range * A.split_len, j_first), j_hi = min(pos, (range + 1) * A.split_len - 1);
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, g = h / (H / G);
+    const int ldk = A.d + kPad, ldv = A.dv + kPad;
+    float* qs = reinterpret_cast<float*>(ss_raw) + h * A.d;
+    float* ws = reinterpret_cast<float*>(ss_raw) + H * A.d;
+    float* tk = ws + H * 32;
+    T* Ks = reinterpret_cast<T*>(tk + H * H);                 // H (d + 32 + H) floats: a multiple of 16 bytes when it matters (vec below)
+    T* Vs = Ks + (size_t)G * 32 * ldk;
+    const int32_t* bt = A.block_table + (size_t)s * A.max_pages;
+    for (int c = lane; c < A.d; c += 32) qs[c] = to_f<T>(qbuf[((size_t)t * H + h) * A.d + c]);
+    for (int c = lane; c < H; c += 32) tk[h * H + c] = S.talk[h * H + c];
+    const float hb = S.head_bias[h];
+    float o[MAXV];
+#pragma unroll
+    for (int e = 0; e < MAXV; ++e) o[e] = 0.0f;
+    // whole 16-byte pieces when every cached row and every staged row starts on a 16-byte boundary
+    const bool vec = (A.d * sizeof(T)) % 16 == 0 && (A.k_off * sizeof(T)) % 16 == 0 && (A.v_off * sizeof(T)) % 16 == 0 &&
+                     ((size_t)H * (A.d + 32 + H) * sizeof(float)) % 16 == 0;
+    const int chunks = vec ? A.d / kPad : A.d;                // dv == d
+    for (int j0 = j_lo; j0 <= j_hi; j0 += 32) {
+        const int cnt = min(32, j_hi - j0 + 1);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < G * cnt * 2 * chunks; idx += blockDim.x) {
+            const int c = idx % chunks, kv = (idx / chunks) & 1, row = (idx / (2 * chunks)) % cnt, gk = idx / (2 * chunks * cnt);
+            const int j = j0 + row;
+            const T* base = pool + (size_t)bt[j / A.page_size] * A.page_elems;
+            const size_t in_pg = (size_t)gk * A.page_size + j % A.page_size;
+            const T* src = kv ? base + A.v_off + in_pg * A.v_ld : base + A.k_off + in_pg * A.k_ld;
+            T* dst = kv ? Vs + ((size_t)gk * 32 + row) * ldv : Ks + ((size_t)gk * 32 + row) * ldk;
+            if (vec) *reinterpret_cast<uint4*>(dst + c * kPad) = *reinterpret_cast<const uint4*>(src + c * kPad);
+            else dst[c] = src[c];
+        }
+        __syncthreads();
+        ws[h * 32 + lane] = lane < cnt ? sigmoidf_(fmaf(key_dot<T>(qs, Ks + ((size_t)g * 32 + lane) * ldk, A.d), A.scale, hb)) : 0.0f;
+        __syncthreads();
+        float mixed = 0.0f;
+        for (int x = 0; x < H; ++x) mixed = fmaf(tk[h * H + x], ws[x * 32 + lane], mixed);
+        const T* vs = Vs + (size_t)g * 32 * ldv;
+        for (int jj = 0; jj < cnt; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, mixed, jj);
+#pragma unroll
+            for (int e = 0; e < MAXV; ++e) {
+                const int c = lane + e * 32;
+                if (c < A.dv) o[e] = fmaf(pj, to_f<T>(vs[jj * ldv + c]), o[e]);
+            }
+        }
+    }
+    float* dst = A.part + ((size_t)blockIdx.x * A.n_splits + blockIdx.y) * (H * A.dv) + h * A.dv;
+#pragma unroll
+    for (int e = 0; e < MAXV; ++e) {
+        const int c = lane + e * 32;
+        if (c < A.dv) dst[c] = o[e];
+    }
+}
+
+// One block per row of a short sequence: adds the ranges' partial sums in range order, applies the head's gate, writes T.
+template <class T>
+__global__ void sigmoid_short_merge_kernel(const SigmoidArgs S, T* __restrict__ out) {
+    const AttnArgs& A = S.a;
+    const int s = blockIdx.x / kShortSeq, r = blockIdx.x % kShortSeq;
+    const int t0 = A.seq_start[s], n = A.seq_start[s + 1] - t0;
+    if (n > kShortSeq || r >= n) return;
+    const int t = t0 + r, pos = A.tok_pos[t], cols = A.H * A.dv;
+    const int ns = pos / A.split_len - sigmoid_first_key(S, pos) / A.split_len + 1;
+    const float* src = A.part + (size_t)blockIdx.x * A.n_splits * cols;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int z = 0; z < ns; ++z) acc += src[(size_t)z * cols + c];
+        out[(size_t)t * A.out_ld + c] = from_f<T>(acc * attn_gate(A, t, c / A.dv, c % A.dv));
     }
 }
 

@@ -425,7 +425,8 @@ def test_large_chunks_split_into_key_ranges(chunk, dtype):
     toks = tokens(1300, 113, 33)
     want = orc.forward(toks)
     b = TokenBatcher(model)
-    got = torch.cat([b.feed([("a", toks[lo:hi], list(range(hi - lo)))]) for lo, hi in ((0, 700), (700, 1290), (1290, 1300))])
+    got = torch.cat([b.feed([("a", toks[lo:hi], list(range(hi - lo)))]) for lo, hi in ((0, 700), (700, 1290), (1290, 1295))] +
+                    [b.feed([("a", [t], [0])]) for t in toks[1295:]])            # a portion of five tokens and single tokens: the few-token form over many ranges
     b.feed([("a", [1], [])], end=["a"])
     assert close_enough(got, want, dtype)
     cuts = [0, 255, 257, chunk - 1, chunk + 16, 1279, 1300]
