@@ -88,6 +88,72 @@ __global__ void residual_norm_kernel(const ResidualArgs A, T* __restrict__ hn, c
     const int D = A.D;
     const size_t o = (size_t)blockIdx.x * D;
     float r1 = A.sy, r2 = A.sy2;
+    if (D <= (int)blockDim.x * kRowRegs) {
+        // the row in registers: every operand is loaded before the first reduction, so a lone row (decoding) waits for
+        // global memory once
+        const bool dyt_r = A.next.w && A.next.kind == SMOL_LM_NORM_DYT;
+        const float alpha_r = dyt_r ? A.next.alpha[0] : 0.0f;
+        float xv[kRowRegs], yv[kRowRegs], zv[kRowRegs], a1[kRowRegs], a2[kRowRegs], e0[kRowRegs], nw[kRowRegs], nb[kRowRegs];
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            const bool in = c < D;
+            xv[i] = in ? A.x[o + c] : 0.0f;
+            yv[i] = (in && A.y) ? A.y[o + c] : 0.0f;
+            zv[i] = (in && A.y2) ? A.y2[o + c] : 0.0f;
+            a1[i] = (in && A.y_w) ? A.y_w[c] : 1.0f;
+            a2[i] = (in && A.y2_w) ? A.y2_w[c] : 1.0f;
+            e0[i] = (in && A.x0) ? A.x0[o + c] : 0.0f;
+            nw[i] = (in && A.next.w) ? A.next.w[c] : 0.0f;
+            nb[i] = (in && dyt_r) ? A.next.shift[c] : 0.0f;
+        }
+        if (A.rs.yp) {
+            for (int k = 0; k < A.rs.top; ++k) {
+                const int slot = A.rs.slot_of[(size_t)blockIdx.x * A.rs.top + k];
+                const float wk = A.rs.sel_w ? A.rs.sel_w[(size_t)blockIdx.x * A.rs.top + k] : 1.0f;
+#pragma unroll
+                for (int i = 0; i < kRowRegs; ++i) {
+                    const int c = threadIdx.x + i * blockDim.x;
+                    if (c < D) xv[i] = fmaf(wk, slot >= 0 ? A.rs.yp[(size_t)slot * D + c] : to_f<T>(hin[o + c]), xv[i]);
+                }
+            }
+        }
+        if (A.y_w || A.y2_w) {
+            float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kRowRegs; ++i) {
+                s1 = fmaf(yv[i], yv[i], s1);
+                s2 = fmaf(zv[i], zv[i], s2);
+            }
+            block_sum3(s1, s2, s3, red3);
+            if (A.y_w) r1 = A.sy / sqrtf(s1 / (float)D + A.eps);
+            if (A.y2_w) r2 = A.sy2 / sqrtf(s2 / (float)D + A.eps);
+            __syncthreads();
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c >= D) continue;
+            float v = fmaf(r2 * a2[i], zv[i], fmaf(r1 * a1[i], yv[i], xv[i]));
+            if (A.trace) A.trace[o + c] = v;
+            v += e0[i];
+            A.x[o + c] = v;
+            xv[i] = v;
+            ss = fmaf(v, v, ss);
+            if (dyt_r) hn[o + c] = from_f<T>(fmaf(tanhf(alpha_r * v), nw[i], nb[i]));
+        }
+        if (!A.next.w || dyt_r) return;
+        float q2 = 0.0f, q3 = 0.0f;
+        block_sum3(ss, q2, q3, red3);
+        const float r = 1.0f / sqrtf(ss / (float)D + A.next.eps);
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < D) hn[o + c] = from_f<T>(xv[i] * r * nw[i]);
+        }
+        return;
+    }
     if (A.y_w || A.y2_w) {
         float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
         for (int c = threadIdx.x; c < D; c += blockDim.x) {

@@ -435,6 +435,28 @@ def test_large_chunks_split_into_key_ranges(chunk, dtype):
     model.check_device_errors()
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_routed_experts_on_every_grouped_product_form(dtype):
+    """Experts wide enough, and steps long enough, for the grouped products' large-tile form (rows copied into sorted order,
+    128-row tiles), the 32-row tile form and the few-pair form of decoding: the same prompt whole, in portions of 40 and
+    token by token."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([hg(heads=2, dim=32, vdim=32, mlp=moe(experts=4, top=2, ff=96, groups=(2, 1), scale=1.2, shared=104)),
+                  par(left(heads=2, kv_heads=1, dim=32, chunk=50, r=rot(32, 100.0)), right(heads=2, dim=16, vdim=16), moe(experts=3, top=1, ff=128, groups=(1, 1), shared=0))],
+                 vocab=101, width=128)
+    model, orc, _ = engine_and_oracle(cfg, seed=13, dtype=dtype, edit=sharp, page_size=64, max_tokens=1024, max_step_tokens=512)
+    toks = tokens(420, 101, 35)
+    want = orc.forward(toks)
+    assert close_enough(run_whole(model, toks), want, dtype)
+    b = TokenBatcher(model)
+    parts = torch.cat([b.feed([("p", toks[lo:lo + 40], list(range(len(toks[lo:lo + 40]))))]) for lo in range(0, 400, 40)] +
+                      [b.feed([("p", [t], [0])]) for t in toks[400:]])
+    b.close()
+    assert close_enough(parts, want, dtype)
+    model.check_device_errors()
+
+
 def random_config(seed):
     """A configuration drawn at random: kinds, sizes, counts and constants all differ from layer to layer."""
     import random
