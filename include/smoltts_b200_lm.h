@@ -163,7 +163,7 @@ typedef struct SmolLmLayer {
     int32_t chunk;
     const float* head_bias;   /* [heads] */
     const float* talk;        /* [heads][heads] fp32 */
-    /* frequency stretching (rot_stretch 0: none): wavelengths 2 pi / f above rot_original / rot_low use f / rot_stretch, those below
+    /* frequency stretching of every rotating mixer (rot_stretch 0: none): wavelengths 2 pi / f above rot_original / rot_low use f / rot_stretch, those below
      * rot_original / rot_high keep f, between them s = (rot_original / wavelength - rot_low) / (rot_high - rot_low) blends
      * (1 - s) f / rot_stretch + s f */
     float rot_stretch, rot_low, rot_high, rot_original;

@@ -1562,7 +1562,8 @@ static bool pairable(const SmolLmLayer& L) {
     return L.mixer == SMOL_LM_MIX_SINK_ATTENTION || L.mixer == SMOL_LM_MIX_STATE_SPACE || L.mixer == SMOL_LM_MIX_SIGMOID_ATTENTION ||
            L.mixer == SMOL_LM_MIX_LIGHTNING;
 }
-// base^(-2i/dims) for the dims/2 rotated pairs, stretched band by band when L.rot_stretch is set (see the header)
+// base^(-2i/dims) for the dims/2 rotated pairs of a latent or sigmoid attention, stretched band by band when L.rot_stretch
+// is set (see the header)
 static void push_frequencies(std::vector<float>& table, const SmolLmLayer& L, bool stretch) {
     const double two_pi = 6.283185307179586476925286766559;
     for (int i = 0; i < L.rot_dims / 2; ++i) {
@@ -1649,7 +1650,7 @@ extern "C" int smol_lm_create(const SmolLmConfig* cfg, const SmolLmLayer* layers
             r.k_off = r.v_off = m->page_elems;
             m->page_elems += (size_t)cfg->page_size * (L.kv_rank + L.rot_dim);
             r.freq_off = m->freq_table.size();
-            push_frequencies(m->freq_table, L, false);
+            push_frequencies(m->freq_table, L, true);
             m->max_q = std::max(m->max_q, L.heads * (L.kv_rank + L.rot_dim));
             m->max_heads = std::max(m->max_heads, L.heads);
             m->max_vdim = std::max(m->max_vdim, L.kv_rank);

@@ -451,7 +451,7 @@ __global__ void sigmoid_short_merge_kernel(const SigmoidArgs S, T* __restrict__ 
 // Needs d % 8 == 0 and 16-byte aligned cached rows.  blockIdx.z is the key range (see SigmoidArgs): a chunk's last rows see
 // many more keys than its first ones, and ranges spread them over the SMs.
 template <int DK, int HPW, int KT>
-__global__ void __launch_bounds__(HPW == 1 ? 512 : 256) sigmoid_flash_kernel(const SigmoidArgs S, const bf16* __restrict__ qbuf,
+__global__ void __launch_bounds__(512) sigmoid_flash_kernel(const SigmoidArgs S, const bf16* __restrict__ qbuf,
                                                                           const bf16* __restrict__ pool, bf16* __restrict__ out) {
     constexpr int LD = DK + 8, LDW = KT + 8;
     extern __shared__ __align__(16) unsigned char sf_smem[];

@@ -45,6 +45,8 @@ LAYERS = {
     "sigmoid-no-rotation": ([par(left(heads=2, kv_heads=1, dim=12, chunk=20, r=rot(0, 10.0, None)))], only_left),
     "sigmoid-wide": ([par(left(heads=2, kv_heads=1, dim=136, chunk=20, scale=0.1, r=rot(64, 500.0)))], only_left),
     "sigmoid-12heads": ([par(left(heads=12, kv_heads=4, dim=8, chunk=3))], only_left),
+    "sigmoid-20heads": ([par(left(heads=20, kv_heads=5, dim=16, chunk=30, r=rot(16)))], only_left),            # two heads per warp in the tiled form
+    "sigmoid-32heads": ([par(left(heads=32, kv_heads=32, dim=24, chunk=25, r=rot(12)))], only_left),
     "lightning": ([par()], only_right),
     "lightning-1head": ([par(r=right(heads=1, dim=32, vdim=8, decay=[0.97]))], only_right),
     "lightning-64x64": ([par(r=right(heads=2, dim=64, vdim=64))], only_right),
