@@ -520,3 +520,21 @@ def test_random_configurations_in_mixed_steps(seed, dtype):
     model.check_device_errors()
     for got, want in ((torch.cat(got_a), want_a), (torch.cat(got_b), want_b)):
         assert close_enough(got, want, dtype)
+
+
+@pytest.mark.parametrize("chunk", [50, 200, 450])
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_decoding_in_a_large_pool(chunk, dtype):
+    """A pool of 40 000 positions: the few-token attention cuts the keys into wider ranges than in a small pool, and a chunk
+    starts inside, at the edge of, or several ranges before the row's own."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([par(left(heads=4, kv_heads=2, dim=16, chunk=chunk, scale=0.5), mlp=dense(32))], vocab=53)
+    model, orc, _ = engine_and_oracle(cfg, seed=15, dtype=dtype, page_size=64, max_tokens=40000, max_step_tokens=512)
+    toks = tokens(520, 53, 6)
+    want = orc.forward(toks)
+    b = TokenBatcher(model)
+    outs = [b.feed([("x", toks[:370], list(range(370)))]), b.feed([("x", toks[370:377], list(range(7)))])]
+    outs += [b.feed([("x", [t], [0])]) for t in toks[377:]]
+    b.close()
+    assert rel_err(torch.cat(outs), want) < TOL[dtype]
