@@ -639,7 +639,10 @@ class LightningSpec:
 
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "LightningSpec":
-        spec = cls(int(d["heads"]), int(d["dim"]), int(d["vdim"]), [float(v) for v in d["decay"]])
+        decay = d["decay"]
+        if isinstance(decay, (int, float)):      # one number: every head's decay
+            decay = [decay] * int(d["heads"])
+        spec = cls(int(d["heads"]), int(d["dim"]), int(d["vdim"]), [float(v) for v in decay])
         if len(spec.decay) != spec.heads:
             raise ValueError("lightning attention: one decay per head")
         return spec

@@ -431,6 +431,8 @@ class TokenBatcher:
                 lo = hi
         outs, traces = [], []
         for part in parts:
+            if not part:                          # a step that only ends requests (or brings no tokens) runs nothing
+                continue
             res = model.forward(part, trace=trace)
             if trace:
                 res, tr = res

@@ -538,3 +538,91 @@ def test_decoding_in_a_large_pool(chunk, dtype):
     outs += [b.feed([("x", [t], [0])]) for t in toks[377:]]
     b.close()
     assert rel_err(torch.cat(outs), want) < TOL[dtype]
+
+
+def model_sized_config(seed, routed=True):
+    """Sizes near a small real model's: widths to 512, up to 20 heads of 32 ... 128 (also sizes the tiled kernels pad),
+    chunks off the page size, up to seven layers with loops of up to four passes."""
+    import random
+
+    r = random.Random(900 + seed)
+
+    def divisor(n):
+        return r.choice([d for d in range(1, n + 1) if n % d == 0])
+
+    def feed():
+        experts = r.choice([4, 6, 8, 12, 16, 24, 32])
+        count = divisor(experts)
+        keep = r.randint(1, count)
+        top = r.randint(1, min(6, keep * (experts // count)))
+        m = moe(experts, top, r.choice([32, 48, 64, 96]), (count, keep), r.uniform(0.5, 2.5), r.choice([0, 32, 64, 128]))
+        return r.choice([None, dense(r.choice([96, 128, 200, 512])), m if routed else dense(72), m if routed else dense(136)])
+
+    layers = []
+    n_layers = r.randint(3, 7)
+    for _ in range(n_layers):
+        if r.random() < 0.3:
+            layers.append(hg(r.choice([1, 2, 4, 6, 8]), r.choice([16, 32, 48, 64, 96, 128]), r.choice([16, 32, 64, 96, 128]), feed()))
+            continue
+        heads = r.choice([2, 4, 5, 8, 10, 12, 16, 20])
+        dim = r.choice([32, 48, 64]) if heads > 16 else r.choice([32, 36, 48, 64, 72, 80, 112, 128])
+        scaling = r.choice([None, (r.choice([2.0, 8.0, 32.0]), r.choice([1.0, 2.0]), r.choice([4.0, 8.0]), r.choice([64, 256, 1024, 8192]))])
+        l = left(heads=heads, kv_heads=divisor(heads), dim=dim, chunk=r.choice([16, 32, 37, 48, 96, 100, 128, 192, 256]),
+                 scale=dim ** -0.5 * r.uniform(0.7, 1.5),
+                 r=rot(2 * r.randint(1, dim // 2) if r.random() < 0.4 else dim, r.choice([100.0, 10000.0, 500000.0]), scaling))
+        sh = r.choice([1, 2, 3, 4, 8])
+        rt = right(heads=sh, dim=r.choice([32, 64, 96, 128]), vdim=r.choice([32, 64, 96, 128]),
+                   decay=[r.choice([0.3, 0.6, 0.9, 0.99, 0.999, 1.0]) for _ in range(sh)])
+        layers.append(par(l, rt, feed()))
+    a = r.randint(0, n_layers - 1)
+    loop = r.choice([None, (a, r.randint(a + 1, n_layers), r.randint(2, 4)), (0, r.randint(1, n_layers), 2)])
+    return config(layers, vocab=r.choice([300, 512, 777, 1000]), width=r.choice([128, 192, 320, 384, 512]), eps=r.choice([1e-6, 1e-5]),
+                  scale=r.uniform(1.0, 16.0), loop=loop)
+
+
+@pytest.mark.parametrize("seed", list(range(4)))
+@pytest.mark.parametrize("dtype", [F32, BF16], ids=["f32", "bf16"])
+def test_model_sized_configurations(seed, dtype):
+    """Random configurations of a small real model's sizes with the engine's default page and step sizes: a whole prompt,
+    decoding, and a second request's portions beside it.  fp32 holds every row; the bf16 engines run the same draw with
+    dense feed-forwards in the routed layers' places (a router's close call is not a matter of sizes)."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = model_sized_config(seed, routed=dtype == F32)
+    model, orc, _ = engine_and_oracle(cfg, seed=40 + seed, dtype=dtype, page_size=64, max_tokens=640, max_step_tokens=2048)
+    V = cfg["vocab"]
+    a, b_ = tokens(260, V, 90 + seed), tokens(150, V, 95 + seed)
+    want_a, want_b = orc.forward(a), orc.forward(b_)
+    tb = TokenBatcher(model)
+    whole = tb.feed([("w", a, list(range(260)))], end=["w"])
+    got_a = [tb.feed([("a", a[:200], list(range(200)))])]
+    got_b = []
+    cuts = [0, 2, 33, 40, 105, 112, 113, 150]
+    for i in range(60):                                   # "a" decodes; "b" arrives in portions beside it, then decodes too
+        entries = [("a", a[200 + i:201 + i], [0])]
+        if i < len(cuts) - 1:
+            entries.append(("b", b_[cuts[i]:cuts[i + 1]], list(range(cuts[i + 1] - cuts[i]))))
+        out = tb.feed(entries)
+        got_a.append(out[:1]); got_b.append(out[1:])
+    tb.close()
+    model.check_device_errors()
+    tol = 6e-4 if dtype == F32 else 8e-2                  # up to nineteen layer runs: fp32 rounding alone reaches a third of this
+    for got, want in ((whole, want_a), (torch.cat(got_a), want_a), (torch.cat(got_b), want_b)):
+        assert rel_err(got, want) < tol
+
+
+def test_a_step_that_only_ends_a_request():
+    """A step may bring no tokens and only end requests: nothing runs, the slot and pages come back and serve the next."""
+    from smoltts_b200.serving import TokenBatcher
+
+    cfg = config([par(mlp=dense(32)), hg(mlp=moe())], vocab=61)
+    model, orc, _ = engine_and_oracle(cfg, seed=3, dtype=F32, page_size=16, max_tokens=64, max_seqs=1)
+    toks = tokens(50, 61, 4)
+    want = orc.forward(toks)
+    tb = TokenBatcher(model)
+    for name in ("x", "y", "x"):
+        got = tb.feed([(name, toks, list(range(50)))])
+        assert tb.feed([], end=[name]).shape == (0, 61)
+        assert rel_err(got, want) < TOL[F32]
+    assert len(model.page_pool) == 4 and len(model.slot_pool) == 1
+    tb.close()

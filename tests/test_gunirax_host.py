@@ -187,3 +187,12 @@ def test_linear_attentions_one_step_at_a_time():
                 keep = keep * f[u]
             o += float(q[t] @ (keep * (1 - f[s]))) * v[s]
         assert float((out[t] - go.rms(o, 1e-6) * w["norm"]).abs().max()) < 1e-12
+
+
+def test_one_decay_number_serves_every_head():
+    cfg = config([par(r=right(heads=3, decay=[0.75, 0.75, 0.75]))])
+    one = copy.deepcopy(cfg)
+    one["layers"][0]["mixer"]["right"]["decay"] = 0.75
+    assert GuniraxConfig.from_dict(one).layers[0].right.decay == GuniraxConfig.from_dict(cfg).layers[0].right.decay == [0.75] * 3
+    with pytest.raises(ValueError):
+        GuniraxConfig.from_dict(config([par(r=right(heads=3, decay=[0.5, 0.5]))]))
