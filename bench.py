@@ -15,11 +15,11 @@ codes, and for N > 1 the host-side gather of every rank's codes on rank 0), for 
 The same line carries ``"configs"``: the other BASELINE.json configurations measured the same way in the same run
 (configs[2] bs=64 sampled, configs[3] bs=256 per GPU at two prompt lengths, configs[4] long-form bs=32 at the
 workload's mean context), each with its own ``roofline`` and ``e2e``, and two entries for the step AFTER the path
-(SURVEY 8(f)-2, the Mimi streaming decoder: ``mimi_bs1``, ``mimi_bs64`` -- codes to PCM, frames/s) and one for the
+(the Mimi streaming decoder: ``mimi_bs1``, ``mimi_bs64`` -- codes to PCM, frames/s) and one for the
 reference's streaming loop through both engines (``tts_stream_bs1``: text to PCM chunks, one frame per host iteration).  Under ``--gpus N > 1`` every entry is the
 per-GPU batch sharded over the N ranks (weak scaling), so the bs=256/GPU 1 -> 8 curve is in the driver's records.
 
-Roofline: algorithmic bytes (SURVEY 8(d): unique weight bytes + KV bytes of the mean context) or flops per launch over
+Roofline: algorithmic bytes (unique weight bytes + KV bytes of the mean context) or flops per launch over
 the CUDA-event duration of the launch, against MEASURED_PEAKS.json; the binding roof (HBM / bf16 tensor) is named.
 ``cpu_baseline``: the oracle port of the reference arithmetic timed on the host cores on a bounded sample taken AT THE
 WORKLOAD'S MEAN CONTEXT (so that ``--impl reference`` measures the same configuration as the GPU arm).
@@ -79,7 +79,7 @@ def headline_work(args) -> Work:
 
 
 def extra_works(model: str):
-    """BASELINE.json configs[2..4] (SURVEY 8(d)), each short enough for the default run."""
+    """BASELINE.json configs[2..4], each short enough for the default run."""
     return [
         Work("config3", model, 64, 256, 200, sampled=True, note="configs[2]: bs=64 sampled, 256 frames"),
         Work("config4i", model, 256, 128, 64, note="configs[3] (i): bs=256 per GPU, 64-byte prompts, 128 frames (tensor-bound regime)"),
@@ -476,7 +476,7 @@ def measure(work: Work, args, steps: int, warmup: int, ctx) -> dict:
 
 
 def measure_mimi(key: str, batch: int, frames: int, args, steps: int, warmup: int, ctx) -> dict:
-    """The step after the path (SURVEY 8(f)-2): Mimi streaming decoder, `batch` streams x `frames` decode_step calls per
+    """The step after the path: Mimi streaming decoder, `batch` streams x `frames` decode_step calls per
     bench step.  value: codes resident in HBM; e2e: codes from pinned host memory, PCM back to pinned host memory, through
     MimiModel.decode_step.  Roofline: every packed fp32 weight once per decode_step + the KV the step touches."""
     import torch
@@ -543,7 +543,7 @@ def measure_mimi(key: str, batch: int, frames: int, args, steps: int, warmup: in
     ach = (wbytes + kv) / (us_step * 1e-6) / 1e9
     res = {
         "key": key, "workload": f"Mimi streaming decoder (kyutai/mimi shape, seeded fp32 weights): {batch} stream(s) x {frames} decode_step calls per step",
-        "note": "SURVEY 8(f)-2: codes [B, 8] -> 1920 fp32 samples per frame; 57 launches per decode_step replayed as one CUDA graph",
+        "note": "codes [B, 8] -> 1920 fp32 samples per frame; 57 launches per decode_step replayed as one CUDA graph",
         "value": steps * frames * batch * world / (total_ms * 1e-3), "unit": "frames/s", "ms_per_step": total_ms / steps, "steps": steps,
         "warmup": warmup, "us_per_frame_step": us_step,
         "roofline": {"bound": "hbm", "achieved": ach, "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "peak_source": src,
@@ -659,7 +659,7 @@ def run_ours(args):
 
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        gloo = dist.new_group(backend="gloo")  # host-side gather of the emitted codes (SURVEY 8(e)); NCCL only times
+        gloo = dist.new_group(backend="gloo")  # host-side gather of the emitted codes; NCCL only times
 
     from smoltts_b200.config import named_config
     from smoltts_b200.synth import make_state_dict

@@ -54,7 +54,7 @@ typedef struct SmolConfig {
     float norm_eps;
 } SmolConfig;
 
-/* One transformer block's parameters: state-dict keys `{layers|fast_layers}.{l}.*` (SURVEY §8(b)). All bf16. */
+/* One transformer block's parameters: state-dict keys `{layers|fast_layers}.{l}.*`. All bf16. */
 typedef struct SmolLayerWeights {
     const void* wqkv;           /* attention.wqkv.weight   [(H+2Hkv)*64, D]  rows q|k|v */
     const void* wo;             /* attention.wo.weight     [D, D] */
@@ -171,8 +171,7 @@ int smol_decode_frames(SmolModel* m, const SmolBatch* b, int32_t batch, const Sm
  * after their logits were produced (NULL switches it off).  Borrowed pointer. */
 int smol_set_force(SmolModel* m, const int32_t* d_force);
 
-/* Runs phases [phase_begin, phase_end) of one frame's program (see smol_phase_count and DESIGN.md
- * "Phase program") - op-level parity tests and per-phase profiling. */
+/* Runs phases [phase_begin, phase_end) of one frame's program (see smol_phase_count) - op-level parity tests and per-phase profiling. */
 int smol_run_phases(SmolModel* m, const SmolBatch* b, int32_t batch, const SmolSampling* s,
                     int32_t phase_begin, int32_t phase_end, void* stream);
 int32_t smol_phase_count(const SmolModel* m);

@@ -1,6 +1,6 @@
 /*
  * smoltts_b200 — C ABI of the B200-native Mimi streaming decoder (codes -> PCM), the step AFTER the DualAR decode
- * step (SURVEY §8(f)-2).  Same library (libsmoltts_b200.so) and conventions as smoltts_b200.h: plain C types, every
+ * step.  Same library (libsmoltts_b200.so) and conventions as smoltts_b200.h: plain C types, every
  * pointer inside the structs / named d_* is a DEVICE pointer owned by the caller, every compute call is asynchronous
  * on the given cudaStream_t (passed as void*), no allocation after create, 0 / negative SMOL_ERR_* return codes with
  * smol_last_error().

@@ -14,10 +14,8 @@ What it follows (paths relative to the reference checkout):
     ``mlx_inference/src/smoltts_mlx/lm/rq_transformer.py:150-220,266-295``,
     ``lm/cache.py:6-22`` and ``lm/generate.py:59-171`` (MLX itself cannot run here).
 
-Pinning: the reference's own tests hold no golden vectors for this path
-(SURVEY §4, §8(c)), so the oracle is pinned against outputs of the reference
-itself: ``tools/make_goldens.py`` imports the unmodified reference from
-/root/reference in the build container, runs ``RQTransformer.forward`` (fp32 and
+Pinning: the reference's own tests hold no golden vectors for this path, so the oracle is pinned against outputs of the reference
+itself: ``tools/make_goldens.py`` imports the unmodified reference, runs ``RQTransformer.forward`` (fp32 and
 bf16) and a literal greedy loop on seeded weights, and commits the results under
 ``tests/golden/``; ``tests/test_oracle_golden.py`` checks this file against them.
 """
@@ -237,7 +235,7 @@ class DualAROracle:
         """grid [B, R, S].  Prefill positions [0, stepwise_from) in one pass, then one
         cached step per position.  Returns token_logits [B, S, V] and
         codebook_logits {t: [B, Nf, C]} for t in fast_positions, where entry i is
-        the logits for grid[:, 1+i, t+1] (SURVEY §3.2 verified mapping)."""
+        the logits for grid[:, 1+i, t+1]."""
         cfg = self.cfg
         B, R, S = grid.shape
         s0 = S if stepwise_from is None else stepwise_from

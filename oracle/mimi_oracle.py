@@ -1,7 +1,7 @@
 """CPU oracle of the Mimi streaming decoder (codes -> PCM) -- TEST INFRASTRUCTURE, never imported by the product.
 
 Restates, with torch CPU fp32 ops, the decode half of the reference's codec
-(`R` = /root/reference/mlx_inference/src/smoltts_mlx/codec/):
+(`R` = the reference's mlx_inference/src/smoltts_mlx/codec/):
 
 * `embed`            R/rvq.py:118-130 (sum of the codebook rows, 1x1 output projection), :171-186 (semantic + acoustic
                      halves), :30-45 (rows = embed_sum / max(cluster_usage, eps))

@@ -1,9 +1,9 @@
 """CPU oracle for the fused sampling kernel.  TEST INFRASTRUCTURE ONLY.
 
-numpy restatement of the sampling specification in DESIGN.md §"Sampling".  The
+numpy restatement of the sampling specification that the CUDA sampler (csrc/sampler.cuh) follows.  The
 reference samples with ``argmax`` (temp == 0) or ``mx.random.categorical(logits /
 temp)`` (mlx_inference/src/smoltts_mlx/lm/generate.py:88-99,118-132); its "min-p"
-branch is a no-op filter (lm/utils/samplers.py:24-28, SURVEY §8(g)-8).  MLX's RNG
+branch is a no-op filter (lm/utils/samplers.py:24-28).  MLX's RNG
 cannot run here, so the *distribution* is what is shared with the reference; the
 bit-exact contract is between this file and the CUDA kernel, which both implement
 the same integer-weight algorithm:

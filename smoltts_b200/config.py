@@ -1,4 +1,4 @@
-"""DualAR model configuration (SURVEY §8 row a1).
+"""DualAR model configuration.
 
 Mirrors the field names, defaults and derivation rules of the reference's
 ``RQTransformerModelArgs`` / ``BaseModelArgs`` dataclasses
@@ -108,7 +108,7 @@ class RQTransformerModelArgs:
         return rows * d + d * d + 3 * d * f
 
     def unique_weight_bytes(self) -> int:
-        """W_unique of SURVEY §8(d): every weight byte a frame must touch, once."""
+        """W_unique: every weight byte a frame must touch, once."""
         head = self.vocab_size * self.dim
         depth_heads = (self.max_fast_seqlen if self.depthwise_output else 1) * self.fast_dim * self.codebook_size
         return 2 * (self.n_layer * self.layer_params() + head
@@ -155,8 +155,8 @@ class RQTransformerModelArgs:
 
 
 # The two configs BASELINE.json names (reference: sample_model_sizes/*.json) plus a
-# tiny one for fast tests.  Values restated here because /root/reference does not
-# travel to the GPU box.
+# tiny one for fast tests.  Values restated here so that the package needs no file of the
+# reference at run time.
 _COMMON = dict(
     attention_qkv_bias=False, codebook_size=2048, dropout=0.1, fast_attention_qkv_bias=False,
     fast_head_dim=64, head_dim=64, initializer_range=1.0 / 24.0, is_reward_model=False,

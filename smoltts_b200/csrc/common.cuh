@@ -61,7 +61,7 @@ __device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uin
 }
 
 // exp(x) * 2^30 truncated to uint32 for x <= 0, IEEE mul/add only (no FMA contraction) so the
-// numpy restatement is bit-identical (DESIGN.md "Sampling").
+// numpy restatement (oracle/sampler_oracle.py) is bit-identical.
 __device__ __forceinline__ uint32_t exp_det_weight(float x) {
     if (!(x >= -21.5f)) return 0u;
     float t = __fmul_rn(x, 1.4426950408889634f);

@@ -3,7 +3,7 @@
 // A frame at batch 1 is a chain of ~200 dependent matrix-vector products; what bounds it is the hand-off between them
 // and the dependent instruction chain inside a CTA, not bytes.  No grid barrier anywhere:
 // every phase publishes 8-byte words {payload | epoch}, consumers poll exactly the words they need, weights stream
-// through a shared-memory ring fed by a TMA producer warp that never waits for activations.  (The round-1 kernel used the
+// through a shared-memory ring fed by a TMA producer warp that never waits for activations.  (The first kernel used the
 // same protocol with CUDA-core GEMVs, one warp per two rows; it is in the git history, ll_kernel.cu.)
 //
 //  * GEMV on the tensor cores.  mma.sync m16n8k16 (bf16 in, fp32 accumulate): the 16 rows of a tile are weight rows,
@@ -14,7 +14,7 @@
 //    split K; a pass carries up to 4 tiles through one K sweep (the B fragments -- the activation -- are loaded once),
 //    partial sums meet in shared memory and are added in warp order by a warp that rotates from pass to pass.
 //    A 16 x 768 tile costs a warp ~15 instructions per 96 elements of K instead of ~200 FMA/unpack instructions per
-//    row pair on the CUDA cores (the round-1 kernel).
+//    row pair on the CUDA cores (the first kernel).
 //  * Everybody polls, nobody computes alone: all 224 consumer threads poll the input vector (16-byte loads, two words
 //    each), every thread normalises four elements in place (RMSNorm: per-warp sums of squares, added in warp order),
 //    so staging + norm are a few instructions per thread instead of one warp's 1 200-cycle chain.

@@ -1,4 +1,4 @@
-// The Mimi streaming decoder (codes -> PCM) for sm_100a: the step after the DualAR decode step (SURVEY §8(f)-2).
+// The Mimi streaming decoder (codes -> PCM) for sm_100a: the step after the DualAR decode step.
 //
 // One frame of one stream: 8 codes -> RVQ rows summed and projected (512) -> 2 upsampled positions -> 8 transformer
 // layers against the stream's KV cache -> SEANet decoder (conv k7, then 4 x [ELU, transposed conv x8/x6/x5/x4, residual

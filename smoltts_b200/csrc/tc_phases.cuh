@@ -616,7 +616,7 @@ __device__ void phase_gemm_tc(const DevModel& M, const CallArgs& A, const Ctx& c
         b1.tm = w_index1 >= 0 ? tm + (size_t)kTensorMapBytes * tm_weight_slot(w_index1, blk) : nullptr;
         b1.row0 = n0; b1.n = w_index1 >= 0 ? blk : 0; b1.box = blk;
         // slow weights are read once per frame (evict first), the depth transformer's by every depth step (keep in L2):
-        // measured DRAM reads 937 -> 891 MB per frame at bs=256, time unchanged (gpurun_out/l2hint_dram.csv)
+        // measured DRAM reads 937 -> 891 MB per frame at bs=256, time unchanged
         umma::tile_mma_tma<kThreads>(ring, bars, pipe, k_len, tm_a, m0, b0, b1, ks * k_len, a_rows,
                                             fast ? SMOL_TC_FAST_POLICY : SMOL_TC_SLOW_POLICY);
         if (prof) { const unsigned long long t = globaltimer_ns(); seg[2] += t - ts; ts = t; }

@@ -5,7 +5,7 @@
 (prefill on the first ``next``, one Mimi frame per ``next``, ``<|im_end|>`` stop rule under
 ``audio_only``, at most ``max_new_tokens + 1`` frames).  Differences, all deliberate:
   * sampling runs on the device with a counter-based RNG; ``top_k`` / ``top_p`` / ``seed`` are
-    added, and ``min_p`` follows the *intended* rule (the reference's is a no-op, SURVEY §8(g)-8)
+    added, and ``min_p`` follows the *intended* rule (the reference's is a no-op)
     only when ``min_p_intended=True``;
   * ``generate_batch`` is new (the reference is bs=1 only): B utterances advance together inside
     one persistent kernel launch per chunk of frames, with the stop rule evaluated on the device.
@@ -138,7 +138,7 @@ def generate_batch(model: RQTransformer, prompts: Sequence[torch.Tensor], genera
 
     Returns a list of int32 tensors: audio_only -> codes [N, T_b] of the audio frames;
     otherwise [1+N, T_b] of every emitted column.  ``fixed_frames`` disables the stop rule
-    (benchmarks: random weights never emit <|im_end|> reliably, SURVEY §8(d))."""
+    (benchmarks: random weights never emit <|im_end|> reliably)."""
     s = generation_settings
     B = len(prompts)
     padded, lens = pack_prompts(model, prompts)

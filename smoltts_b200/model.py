@@ -1,6 +1,6 @@
 """Host side of the DualAR decode engine: checkpoint loading and the model-level calls.
 
-Mirrors the reference's surfaces for this path (SURVEY §8(b)):
+Mirrors the reference's surfaces for this path:
   * ``RQTransformer.from_pretrained(path, load_weights, weight_override, max_length, rope_base)``
     -- reference modeling/model/rq_transformer.py:273-319 (state-dict keys, config, tokenizer ids);
   * ``forward_generate(inputs, cache) -> (token_logits, hidden)`` and
@@ -267,7 +267,7 @@ class RQTransformer:
         return {k: v for k, v in self.weights.items() if not k.startswith("__")}
 
     def save_pretrained(self, pathname: str) -> None:
-        """config.json + model.safetensors in the exported layout (SURVEY §8(b))."""
+        """config.json + model.safetensors in the exported layout."""
         from safetensors.torch import save_file
 
         os.makedirs(pathname, exist_ok=True)

@@ -1,4 +1,4 @@
-"""Front end of the decode path (SURVEY §8(f)-3): prompt encoding and continuous batching.
+"""Front end of the decode path: prompt encoding and continuous batching.
 
 ``PromptEncoder`` mirrors the reference's encoder (mlx_inference/src/smoltts_mlx/lm/utils/prompt.py:10-63) and the
 prompt assembly of ``SmolTTS`` (mlx_inference/src/smoltts_mlx/__init__.py:97-151) on torch int64 grids ``[1+N', S]``;

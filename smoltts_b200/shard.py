@@ -1,4 +1,4 @@
-"""Utterance sharding across the GPUs of one box (SURVEY §8(e)).
+"""Utterance sharding across the GPUs of one box.
 
 The decode path has no cross-utterance term, so multi-GPU is plain data parallelism: every rank owns
 a full weight replica, a private KV pool and a contiguous slice of the utterances; there is no
@@ -100,8 +100,7 @@ def _worker_main(rank: int, spec: dict, factory, run, tasks, results):
 
 
 class ShardedGenerator:
-    """``gpus`` worker processes, each with a full weight replica and a private KV pool on its own GPU (SURVEY 8(e):
-    the path shards by utterance, no collective on the decode path).  ``generate`` gives worker r the contiguous
+    """``gpus`` worker processes, each with a full weight replica and a private KV pool on its own GPU (the path shards by utterance, no collective on the decode path).  ``generate`` gives worker r the contiguous
     slice ``partition(len(prompts), gpus)[r]`` (``seq_id`` = global utterance index, so sampling does not depend on
     the sharding) and returns every utterance's codes in the caller's order."""
 

@@ -1,4 +1,4 @@
-"""Synthetic weights, prompts and token grids (SURVEY §8(d) "Synthetic inputs").
+"""Synthetic weights, prompts and token grids.
 
 There is no network for checkpoints or datasets, so benchmarks and parity tests
 use seeded random-init weights of the reference architecture and synthetic
@@ -41,8 +41,7 @@ def _normal(name: str, shape, std: float, seed: int) -> torch.Tensor:
 
 
 def state_dict_shapes(cfg: RQTransformerModelArgs, flat_fast_output: bool = True) -> Dict[str, tuple]:
-    """Key -> shape of the exported checkpoint (SURVEY §8(b) "Checkpoint layout";
-    reference state_dict of modeling/model/rq_transformer.py + train/convert_safetensors.py:6-16)."""
+    """Key -> shape of the exported checkpoint (reference state_dict of modeling/model/rq_transformer.py + train/convert_safetensors.py:6-16)."""
     D, F, V = cfg.dim, cfg.intermediate_size, cfg.vocab_size
     Df, Ff = cfg.fast_dim, cfg.fast_intermediate_size
     C, N = cfg.codebook_size, cfg.num_codebooks
@@ -83,8 +82,7 @@ def make_state_dict(cfg: RQTransformerModelArgs, seed: int = 0, flat_fast_output
     reference's ``_init_weights`` does (rq_transformer.py:262-271); norm weights 1
     (optionally jittered so tests exercise the multiply); ``fast_output.weight``
     re-drawn N(0, initializer_range) because the reference leaves it at
-    kaiming-uniform over a 3-D tensor, which makes codebook logits degenerate
-    (SURVEY §7.1-0).  ``fast_output`` is always *generated* in the flat exported
+    kaiming-uniform over a 3-D tensor, which makes codebook logits degenerate.  ``fast_output`` is always *generated* in the flat exported
     layout [(i*C + k), D] and reshaped for the 3-D trainer form on request."""
     std = cfg.initializer_range
     out: Dict[str, torch.Tensor] = {}
@@ -139,8 +137,7 @@ def prompt_grid(row0: List[int], cfg: RQTransformerModelArgs) -> torch.Tensor:
 def teacher_grid(cfg: RQTransformerModelArgs, n_text: int, n_audio: int, batch: int = 1,
                  seed: int = 7, zero_code_at: Optional[int] = None) -> torch.Tensor:
     """Random teacher-forcing grid [B, 1+N', n_text+n_audio]: text columns then audio
-    columns with row0 = 320 + first depth code (dup0) as real data has
-    (SURVEY §8(c) protocol 1).  ``zero_code_at`` forces row-1 code 0 at one audio
+    columns with row0 = 320 + first depth code (dup0) as real data has.  ``zero_code_at`` forces row-1 code 0 at one audio
     column to exercise the PyTorch embed-mask quirk (§8(g)-1)."""
     g = torch.Generator(device="cpu")
     g.manual_seed(seed)
@@ -160,7 +157,7 @@ def teacher_grid(cfg: RQTransformerModelArgs, n_text: int, n_audio: int, batch: 
     return grid
 
 
-# ---- Mimi decoder (SURVEY §8(f)-2): seeded weights under kyutai/mimi's state-dict keys ----------------------------------
+# ---- Mimi decoder: seeded weights under kyutai/mimi's state-dict keys ----------------------------------
 def mimi_state_dict_shapes(n_q: int = 8, codebook_size: int = 2048, codebook_dim: int = 256, dim: int = 512, n_layers: int = 8,
                            ffn: int = 2048, n_filters: int = 64, ratios=(8, 6, 5, 4), kernel: int = 7, res_kernel: int = 3,
                            last_kernel: int = 3) -> Dict[str, tuple]:

@@ -61,7 +61,7 @@ class SmolTTS:
         ``SingleBatchGenerator.__next__`` (launch, host read-back), then the codec step, then the chunk.  ``overlap`` (default)
         keeps both engines busy: the decode step of frame t + 1 is launched BEFORE the host looks at frame t, and frame t's ids,
         its codec step and its PCM go through a side stream -- the data-flow kernel is told to take ``lm_ctas`` of the GPU's SMs (a
-        bs=1 frame takes the same 600-612 us on 96 .. 148 CTAs, DESIGN.md section 4), the codec's kernels run on the others.
+        bs=1 frame takes the same 600-612 us on 96 .. 148 CTAs), the codec's kernels run on the others.
         Throughput is then bound by the slower engine instead of the sum plus the host's time per frame.  Same chunks, bit for bit."""
         prompt = self._get_prompt(input, voice if voice is not None else "0")
         codec = self.codec

@@ -61,7 +61,7 @@ def test_config3_bs64_sampled_ids_follow_the_sampler_spec():
 def test_config4_bs256_shards_are_independent():
     cfg, sd, model, orc = model_and_oracle("smoltts_byte_150m", max_batch=256, max_seq_len=128)
     B, n_frames = 256, 2
-    prompts = [prompt_grid(byte_prompt(64, seed=1 + b), cfg) for b in range(B)]   # the 64-byte-prompt point of SURVEY 8(d)
+    prompts = [prompt_grid(byte_prompt(64, seed=1 + b), cfg) for b in range(B)]   # the 64-byte-prompt point
     gs = GenerationSettings(default_temp=0.0, default_fast_temp=0.0)
     whole = generate_batch(model, prompts, gs, audio_only=False, fixed_frames=n_frames, seq_ids=list(range(B)))
     shard1 = generate_batch(model, prompts[128:], gs, audio_only=False, fixed_frames=n_frames, seq_ids=list(range(128, B)))

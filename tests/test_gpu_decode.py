@@ -1,6 +1,6 @@
 """Frame-level parity on the GPU, through the C-ABI.
 
-Tolerances are calibrated, not guessed (DESIGN.md "Parity"): on these seeded
+Tolerances are calibrated, not guessed: on these seeded
 random-init weights the reference's own eager bf16 forward differs from its fp32 forward by
 rms 0.035 / 0.056 (token / codebook logits, 150m) and two bf16 executions that only differ in GEMM
 shape differ by up to 0.19.  The north star's example (max-abs 2e-2) is tighter than the reference is

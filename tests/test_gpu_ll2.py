@@ -88,7 +88,7 @@ def test_ll2_long_context_blocks(size, n_prompt):
 
 
 def test_ll2_depth7_without_duplicate_code_0():
-    """duplicate_code_0 = False (the kokoro_v1 data config, SURVEY 8(g)-6): 7 depth steps, shifted embedding offsets -- against
+    """duplicate_code_0 = False (the kokoro_v1 data config): 7 depth steps, shifted embedding offsets -- against
     the barrier kernel through forced ids: the two kernels sum in different orders, so logits are compared, not bits."""
     cfg, sd, model, orc = model_and_oracle("smoltts_byte_tiny", max_batch=1, duplicate_code_0=False)
     assert cfg.max_fast_seqlen == 7

@@ -46,7 +46,7 @@ def test_slow_layer_phases_match_oracle_trace(size, B, T):
     # (pre-RoPE value, residual operand) seen through a cancellation: at most 0.02 % of a tensor's elements, each within one
     # bf16 ulp of the tensor's largest value (measured: 1 element of 2304 at 4 ulps of itself)
     _OUTLIERS["frac"] = 2e-4 if B >= 16 else 0.0
-    # B == 3: the traced column itself has row-1 code 0 (PyTorch embed-mask quirk, SURVEY 8(g)-1)
+    # B == 3: the traced column itself has row-1 code 0 (PyTorch embed-mask quirk)
     grid = teacher_grid(cfg, n_text=T - 6, n_audio=8, batch=B, seed=11, zero_code_at=6 if B == 3 else 2)  # [B, R, T+2]
     with torch.no_grad():
         cache = orc.new_cache()
@@ -93,7 +93,7 @@ def test_slow_layer_phases_match_oracle_trace(size, B, T):
             # product and sum the unrounded ones; what remains is the order of the running-max updates (per position /
             # per 16 positions here, per 512-position block there) and exp itself.
             # Measured on B200: tensor-core batch attention (B >= 9) 0.84 .. 0.89 bit-exact on 70m / 150m, 0.71 .. 0.89 on tiny;
-            # CUDA-core split-KV attention of the barrier kernel (running maximum per position) 0.53 .. 0.81; round 1 (P kept
+            # CUDA-core split-KV attention of the barrier kernel (running maximum per position) 0.53 .. 0.81; the first build (P kept
             # in fp32): 0.40 .. 0.60.
             ex, mu = close_report(tag + "attn", abuf[:, :D], trace[tag + "attn"], max_ulp=3.0, min_exact=0.65 if B >= 9 else 0.50)
             print(f"{size} B={B} {tag}attn: {ex:.3f} bit-exact, max {mu:.1f} ulps")

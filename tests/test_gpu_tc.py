@@ -3,7 +3,7 @@
 Its dot products are summed by the tensor core, so it is not bit-identical to the CUDA-core variants; it is held to
   * the oracle's greedy ids up to near-tie decisions (greedy-with-resync, same rule and TAU as tests/test_gpu_decode.py);
   * the CUDA-core variant's logits and cached K/V on the same inputs, within the spread the reference's own bf16
-    executions show (rms 0.035 / 0.056 on token / codebook logits, DESIGN.md section 6);
+    executions show (rms 0.035 / 0.056 on token / codebook logits);
   * bit-identity with itself across launch modes (persistent kernel == per-phase CUDA graph), batch compositions and
     prefill tile sizes.
 """
@@ -212,7 +212,7 @@ def test_tc_stop_rule_and_sampling_inside_a_batch():
 
 
 def test_tc_depth7_without_duplicate_code_0():
-    """duplicate_code_0 = False (7 depth steps, shifted embedding offsets, SURVEY 8(g)-6) on the tensor-core variant:
+    """duplicate_code_0 = False (7 depth steps, shifted embedding offsets) on the tensor-core variant:
     16 utterances greedy-with-resync against the oracle."""
     cfg, sd, model, orc = model_and_oracle("smoltts_byte_tiny", max_batch=16, duplicate_code_0=False)
     assert cfg.max_fast_seqlen == 7

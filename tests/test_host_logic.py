@@ -26,7 +26,7 @@ def test_config_derivation_follows_the_reference_rules():
     assert c2.extra == {"unknown_key": 3} and c2.to_dict()["unknown_key"] == 3
 
 
-def test_roofline_denominators_match_the_survey():
+def test_roofline_denominators():
     c150, c70 = named_config("smoltts_byte_150m"), named_config("smoltts_byte_70m")
     assert c150.layer_params() == 8_650_752
     assert c150.unique_weight_bytes() == 271_024_128

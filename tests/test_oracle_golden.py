@@ -1,9 +1,9 @@
 """Pins oracle/dualar_oracle.py against outputs of the UNMODIFIED reference.
 
 tests/golden/*.npz were produced by tools/make_goldens.py, which imports
-/root/reference/modeling (RQTransformer.forward, fp32 + bf16, and a literal greedy
+the reference's modeling package (RQTransformer.forward, fp32 + bf16, and a literal greedy
 loop through the same forward).  The reference's own tests hold no vectors for this
-path (SURVEY §4), so these files are what pins the restatement.
+path, so these files are what pins the restatement.
 """
 import hashlib
 

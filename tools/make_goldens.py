@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Generate tests/golden/*.npz from the UNMODIFIED reference (build container only).
 
-Imports ``modeling.model.rq_transformer`` from /root/reference (read-only, eager:
+Imports ``modeling.model.rq_transformer`` from the reference checkout named by SMOLTTS_REFERENCE (read-only, eager:
 TORCHDYNAMO_DISABLE=1 because its @torch.compile sites cannot build here), loads the
 seeded synthetic weights of ``smoltts_b200.synth`` into it, and records
   * teacher-forced ``RQTransformer.forward`` logits in fp32 and bf16
@@ -9,8 +9,8 @@ seeded synthetic weights of ``smoltts_b200.synth`` into it, and records
   * a literal greedy decode driven through the same ``forward`` (9 full forwards
     per frame: 1 for the slow token, then one per depth code through a
     provisional column), bf16 and fp32, with the top-2 margin of every decision.
-The reference cannot travel to the GPU box, so these vectors are what pins
-``oracle/dualar_oracle.py`` (SURVEY §8(c)).
+The reference is not available where the GPU tests run, so these vectors are what pins
+``oracle/dualar_oracle.py``.
 
 usage: TORCHDYNAMO_DISABLE=1 python tools/make_goldens.py [--sizes tiny 70m 150m]
 """
@@ -25,7 +25,7 @@ import tempfile
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, "/root/reference")
+sys.path.insert(0, os.environ["SMOLTTS_REFERENCE"])  # checkout of the reference
 
 import numpy as np  # noqa: E402
 import torch  # noqa: E402

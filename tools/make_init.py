@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Fabricate a checkpoint directory for a named model size: ``config.json``,
 byte-level tokenizer files and seeded random ``model.safetensors`` in the
-reference's exported layout (SURVEY §7.1-0, §8(b)).
+reference's exported layout.
 
 The tokenizer follows the recipe of the reference's
 data_pipeline/scripts/create_bytelevel_init.py:15-57 (256 byte tokens, 15 control

@@ -1,9 +1,9 @@
 #!/usr/bin/env python
 """Condenses one kernel of an `ncu --set full` report into the two files committed under profiles/:
 <prefix>_ncu_full_details.csv (ncu --page details --csv of that kernel) and <prefix>_ncu_summary.json (the counters
-DESIGN.md / bench.py quote + the stall-reason shares of the warp-state samples).
+bench.py quotes + the stall-reason shares of the warp-state samples).
 
-usage: python tools/summarize_ncu.py gpurun_out/x.ncu-rep <kernel id in the report> profiles/<prefix> [note]
+usage: python tools/summarize_ncu.py x.ncu-rep <kernel id in the report> profiles/<prefix> [note]
 """
 import csv
 import io
